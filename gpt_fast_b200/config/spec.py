@@ -1,0 +1,69 @@
+"""Data that describes a model to build: which parts, with which sizes and
+constants, in which order.
+
+Nothing here knows an architecture.  An architecture (see `registry.py`)
+turns its typed configuration into a `ModelSpec`; `engine.model.Transformer`
+builds itself from the spec alone.  Every size a part needs is in its
+`PartSpec.params`; the order in which layers run is the `schedule` list.
+"""
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """One part: `kind` is a key of the matching registry in `parts`, `params`
+    are the constructor's keyword arguments (sizes and constants only)."""
+    kind: str
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One set of layer parameters.  `block` names the arrangement of the
+    parts (for instance pre-norm residual); each layer picks its own mixer,
+    feed-forward and norms, so layers of one model may differ."""
+    block: str
+    mixer: PartSpec
+    feed_forward: PartSpec
+    mixer_norm: PartSpec
+    ffn_norm: PartSpec
+    position: Optional[PartSpec] = None   # position encoding the mixer applies
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One run of a layer.  `layer` indexes `ModelSpec.layers` (a layer may be
+    named by several entries: its weights are then shared).  `cache` is the id
+    of the cache entry the run's mixer uses; with `owns_cache=False` the run
+    appends nothing and reads what the entry's owner wrote earlier in the
+    same step."""
+    layer: int
+    cache: int
+    owns_cache: bool = True
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    dim: int
+    vocab_size: int
+    layers: List[LayerSpec]
+    schedule: List[ScheduleEntry]
+    final_norm: PartSpec
+    tie_embeddings: bool = False
+    max_position: int = 0                 # longest sequence the model allows
+    stop_tokens: tuple = ()               # default stop tokens of generation
+    bos_token: Optional[int] = None
+
+    def validate(self) -> None:
+        owners = {}
+        for i, e in enumerate(self.schedule):
+            if not 0 <= e.layer < len(self.layers):
+                raise ValueError(f"schedule[{i}] names layer {e.layer}, the model has {len(self.layers)}")
+            if e.owns_cache:
+                if e.cache in owners:
+                    raise ValueError(f"cache entry {e.cache} has two owners: schedule[{owners[e.cache]}] and [{i}]")
+                owners[e.cache] = i
+            elif e.cache not in owners:
+                raise ValueError(f"schedule[{i}] reads cache entry {e.cache} before any run wrote it")

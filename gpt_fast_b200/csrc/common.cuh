@@ -1,0 +1,121 @@
+// Shared declarations of the sm_100a kernel libraries.
+//
+// Every library exports plain C functions (called from Python through ctypes):
+// raw device pointers, sizes, a stream; the return value is 0 on success and
+// `gfb_last_error()` of the same library then explains a failure.  Kernels
+// never trap: a condition found on the device (token id out of range, a
+// position beyond the cache, a wait that ran out) is written to the caller's
+// `status` words and the offending access is skipped.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define GFB_API extern "C" __attribute__((visibility("default")))
+
+// element types of tensors that come in two precisions
+enum { GFB_F32 = 0, GFB_BF16 = 1 };
+
+// device status codes: status[0] = first code seen, status[1..3] = details
+enum {
+    GFB_OK = 0,
+    GFB_ERR_TOKEN_RANGE = 1,      // status[1] = token index, status[2] = id
+    GFB_ERR_CACHE_RANGE = 2,      // status[1] = token index, status[2] = position
+    GFB_ERR_WAIT_TIMEOUT = 3,     // status[1] = which wait, status[2] = block
+    GFB_ERR_PAGE_TABLE = 4,       // status[1] = slot, status[2] = page index
+};
+
+__device__ __forceinline__ void gfb_report(int* status, int code, int a, int b) {
+    if (status != nullptr && atomicCAS(status, 0, code) == 0) {
+        status[1] = a;
+        status[2] = b;
+    }
+}
+
+// ---- host side error text ----------------------------------------------------
+static thread_local char gfb_error_text[512] = "";
+
+static inline int gfb_fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(gfb_error_text, sizeof(gfb_error_text), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+static inline int gfb_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return gfb_fail("%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+#define GFB_DEFINE_LAST_ERROR() \
+    GFB_API const char* gfb_last_error() { return gfb_error_text; }
+
+// ---- conversions ---------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float gfb_to_f32(T v);
+template <> __device__ __forceinline__ float gfb_to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float gfb_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T gfb_from_f32(float v);
+template <> __device__ __forceinline__ float gfb_from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 gfb_from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- deterministic block reductions (fixed tree, result in every thread) ---------
+__device__ __forceinline__ float gfb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float gfb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// `scratch` needs 32 floats of shared memory; blockDim.x must be a multiple of 32.
+__device__ __forceinline__ float gfb_block_sum(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = gfb_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarp) ? scratch[lane] : 0.f;
+    return gfb_warp_sum(r);
+}
+__device__ __forceinline__ float gfb_block_max(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = gfb_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarp) ? scratch[lane] : -INFINITY;
+    return gfb_warp_max(r);
+}
+
+// ---- the batch of one step, as kernels see it --------------------------------------
+// n sequences, T packed tokens.  Token t belongs to sequence tok_seq[t]; the
+// sequence's tokens are cu_seqlens[s] .. cu_seqlens[s+1]-1; its cache slot is
+// slots[s]; lengths[slot] tokens were cached BEFORE this step, so token t sits
+// at position lengths[slot] + (t - cu_seqlens[s]).
+struct GfbBatch {
+    const int* cu_seqlens;   // [n+1]
+    const int* tok_seq;      // [T]
+    const int* slots;        // [n]
+    const int* lengths;      // [n_slots]
+    int n_seqs;
+    int n_tokens;
+};
+
+// Paged key/value storage of one cache entry: page p of a pool holds
+// [n_kv][page_size][head_dim]; page_table[slot][i] is the page that holds the
+// slot's positions i*page_size .. (i+1)*page_size-1.
+struct GfbPagedKV {
+    void* k_pool;
+    void* v_pool;
+    const int* page_table;   // [n_slots][max_pages]
+    int max_pages;
+    int page_size;
+    int n_pages;
+};

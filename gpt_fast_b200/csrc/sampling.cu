@@ -1,0 +1,182 @@
+// Next-token choice on the device, one block per row of 32-bit logits.
+//
+// gpt-fast's sample() (generate.py:40-57): logits / max(temperature, 1e-5);
+// with top_k, everything below the k-th largest value becomes -inf (ties with
+// it are kept); softmax; then the exponential race argmax(p / q), q ~ Exp(1),
+// which draws from p without a host synchronisation.  Here the same steps run
+// in one kernel: the k-th largest value comes from a 4-pass radix select over
+// the order-preserving integer image of the floats, and q comes from
+// Philox4x32-10 keyed by (seed; request id, token index, vocabulary index), so
+// a request draws the same tokens alone or in any batch.  The softmax
+// denominator is the same for every candidate and is left out of the argmax.
+// Greedy choice (temperature 0 in this library) is a plain argmax, lowest
+// index on ties.
+#include "common.cuh"
+
+GFB_DEFINE_LAST_ERROR()
+
+constexpr int THREADS = 512;
+
+__device__ __forceinline__ uint32_t float_key(float x) {       // ascending order of floats
+    uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+    uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(u);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                              uint32_t k0, uint32_t k1, uint32_t out[4]) {
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+        uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// Exp(1) noise for (request, token index, vocabulary index): -log(u), u in (0,1)
+__device__ __forceinline__ float race_noise(uint64_t seed, int64_t request, int token_index, int i) {
+    uint32_t r[4];
+    philox4x32_10((uint32_t)i, (uint32_t)token_index, (uint32_t)(uint64_t)request, (uint32_t)((uint64_t)request >> 32),
+                  (uint32_t)seed, (uint32_t)(seed >> 32), r);
+    float u = ((float)(r[0] >> 9) + 0.5f) * (1.0f / 8388608.0f);
+    return -logf(u);
+}
+
+// argmax over (value, index) pairs, larger value wins, lower index on ties
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+__device__ int block_argmax(float v, int i, float* sv, int* si) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        argmax_combine(v, i, ov, oi);
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) { sv[warp] = v; si[warp] = i; }
+    __syncthreads();
+    if (warp == 0) {
+        int nw = blockDim.x >> 5;
+        v = lane < nw ? sv[lane] : -INFINITY;
+        i = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            int oi = __shfl_xor_sync(0xffffffffu, i, o);
+            argmax_combine(v, i, ov, oi);
+        }
+        if (lane == 0) si[0] = i;
+    }
+    __syncthreads();
+    return si[0];
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+        float x = row[i];
+        if (x != x) x = -INFINITY;              // NaN never wins
+        argmax_combine(v, idx, x, i);
+    }
+    int best = block_argmax(v, idx, sv, si);
+    if (threadIdx.x == 0) out[blockIdx.x] = best == 0x7fffffff ? 0 : best;
+}
+
+// temperature / top-k / exponential race.  The token index of row b is
+// token_index[index_map[b]] (index_map optional).  noise_out (optional, [B,V]) receives q.
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temp, int top_k,
+              uint64_t seed, const int64_t* __restrict__ request_ids, const int* __restrict__ token_index,
+              const int* __restrict__ index_map, float* __restrict__ noise_out) {
+    __shared__ unsigned int hist[256];
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ uint32_t sh_prefix;
+    __shared__ int sh_remaining;
+    const float* row = logits + (size_t)blockIdx.x * V;
+
+    // pivot = k-th largest scaled logit (everything when top_k <= 0 or >= V)
+    float pivot = -INFINITY;
+    if (top_k > 0 && top_k < V) {
+        uint32_t prefix = 0, mask = 0;
+        int remaining = top_k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int i = threadIdx.x; i < 256; i += THREADS) hist[i] = 0;
+            __syncthreads();
+            for (int i = threadIdx.x; i < V; i += THREADS) {
+                uint32_t k = float_key(row[i] / temp);
+                if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int left = remaining, bin = 255;
+                for (; bin > 0; bin--) {
+                    int c = (int)hist[bin];
+                    if (c >= left) break;
+                    left -= c;
+                }
+                sh_prefix = prefix | ((uint32_t)bin << shift);
+                sh_remaining = left;
+            }
+            __syncthreads();
+            prefix = sh_prefix;
+            remaining = sh_remaining;
+            mask |= 255u << shift;
+            __syncthreads();
+        }
+        pivot = key_float(prefix);
+    }
+
+    // the largest scaled logit is always kept
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += THREADS) m = fmaxf(m, row[i] / temp);
+    m = gfb_block_max(m, sv);
+
+    int64_t request = request_ids ? request_ids[blockIdx.x] : (int64_t)blockIdx.x;
+    int tix = token_index ? token_index[index_map ? index_map[blockIdx.x] : blockIdx.x] : 0;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+        float x = row[i] / temp;
+        float qn = race_noise(seed, request, tix, i);
+        if (noise_out) noise_out[(size_t)blockIdx.x * V + i] = qn;
+        if (x >= pivot) {
+            float score = expf(x - m) / qn;
+            argmax_combine(best, best_i, score, i);
+        }
+    }
+    int winner = block_argmax(best, best_i, sv, si);
+    if (threadIdx.x == 0) out[blockIdx.x] = winner == 0x7fffffff ? 0 : winner;
+}
+
+GFB_API int gfb_argmax(const float* logits, int* out, int B, int V, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (V <= 0) return gfb_fail("gfb_argmax: V = %d", V);
+    argmax_kernel<<<B, THREADS, 0, stream>>>(logits, out, V);
+    return gfb_check_launch("gfb_argmax");
+}
+
+GFB_API int gfb_sample(const float* logits, int* out, int B, int V, float temperature, int top_k,
+                       unsigned long long seed, const long long* request_ids, const int* token_index,
+                       const int* index_map, float* noise_out, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (V <= 0) return gfb_fail("gfb_sample: V = %d", V);
+    float t = temperature > 1e-5f ? temperature : 1e-5f;
+    sample_kernel<<<B, THREADS, 0, stream>>>(logits, out, V, t, top_k, (uint64_t)seed,
+                                             (const int64_t*)request_ids, token_index, index_map, noise_out);
+    return gfb_check_launch("gfb_sample");
+}

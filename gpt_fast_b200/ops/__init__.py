@@ -1,0 +1,124 @@
+"""The operations a model step is made of, each one a hand-written sm_100a
+kernel (sources under `csrc/`).
+
+Parts call the functions of this module; the functions check shapes and
+types on the host, pick the kernel that fits (tensor-core kernels for aligned
+bfloat16 shapes, the generic kernels otherwise and for 32-bit) and launch it
+on the current CUDA stream.  There is no CPU or library fallback: if the
+kernel libraries cannot be built or the tensors are not on a CUDA device, the
+call raises.  `kernels()` returns the object that implements the operations;
+tests may put a stand-in there with `use_kernels` to exercise the host-side
+logic without a GPU.
+"""
+from typing import Optional
+
+import torch
+
+from .types import BatchMeta, PagedKV
+
+STATUS_WORDS = 4
+_STATUS_TEXT = {
+    1: "token id out of range (token index {a}, id {b})",
+    2: "position beyond the cache or the rotary table (token index {a}, position {b})",
+    3: "a device-side wait ran out (wait {a}, block {b})",
+    4: "page table has no page there (slot {a}, page index {b})",
+}
+
+_kernels = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def kernels():
+    global _kernels
+    if _kernels is None:
+        from .cuda import CudaKernels
+        _kernels = CudaKernels()
+    return _kernels
+
+
+def use_kernels(obj):
+    """Replace the kernel object (a test seam); returns the previous one."""
+    global _kernels
+    prev, _kernels = _kernels, obj
+    return prev
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(STATUS_WORDS, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Read the device-side error words (this synchronises) and raise if a
+    kernel reported something; the words are cleared afterwards."""
+    s = status.tolist()
+    if s[0] != 0:
+        status.zero_()
+        text = _STATUS_TEXT.get(s[0], "device error code {c}").format(a=s[1], b=s[2], c=s[0])
+        raise KernelError(f"a kernel reported: {text}")
+
+
+# ---- the operations ---------------------------------------------------------------
+
+def embed(tokens, table, out, status):
+    """out[t] = table[tokens[t]] widened to 32-bit.  tokens int32 [T]; table
+    [V, D]; out float32 [T, D]."""
+    return kernels().embed(tokens, table, out, status)
+
+
+def rmsnorm(x, weight, eps: float, out, rows=None):
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight.  x float32
+    [T, D]; weight [D] (bfloat16 or float32); out [R, D]; rows int32 [R] or None."""
+    return kernels().rmsnorm(x, weight, eps, out, rows)
+
+
+def linear(a, w, out, mode: str = "store"):
+    """a [M, K] times w [N, K] transposed.  mode 'store': out [M, N] = product;
+    'add': out float32 [M, N] += product (the residual sum, in 32-bit);
+    'swiglu': w's rows alternate gate, up and out [M, N/2] = silu(gate) * up."""
+    return kernels().linear(a, w, out, mode)
+
+
+def rope_table(inv_freq, table):
+    """table[p, i] = (cos, sin)(p * inv_freq[i]) in 32-bit.  table float32 [P, d/2, 2]."""
+    return kernels().rope_table(inv_freq, table)
+
+
+def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n_kv: int, head_dim: int,
+                pairing: str = "interleaved", append: bool = True):
+    """Rotate the q and k heads of qkv [T, (H+2G)d] by each token's position;
+    q goes to q_out [T, H, d]; k and v go to the token's place in the cache
+    (unless append is False)."""
+    return kernels().rope_append(qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing, append)
+
+
+def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, head_dim: int, scale: float,
+              window: Optional[int] = None):
+    """Causal grouped-query attention of q [T, H, d] over the cache (which
+    already holds this step's keys and values); out [T, H*d]."""
+    return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
+
+
+def advance_lengths(batch: BatchMeta):
+    """lengths[slot] += number of new tokens, for every sequence of the batch."""
+    return kernels().advance_lengths(batch)
+
+
+def add_into(out, y):
+    """out (float32) += y."""
+    return kernels().add_into(out, y)
+
+
+def argmax(logits, out):
+    """out[b] = index of the largest logits[b, :], lowest index on ties."""
+    return kernels().argmax(logits, out)
+
+
+def sample(logits, out, temperature: float, top_k: Optional[int], seed: int, request_ids=None, token_index=None,
+           index_map=None, noise_out=None):
+    """Temperature / top-k / exponential-race draw per row of float32 logits.
+    The noise of row b is keyed by (seed, request_ids[b], token_index[index_map[b]
+    or b], vocabulary index), so it does not depend on the row's place in the batch."""
+    return kernels().sample(logits, out, temperature, top_k, seed, request_ids, token_index, index_map, noise_out)

@@ -1,0 +1,189 @@
+"""ctypes bindings of the kernel libraries: host-side checks, kernel choice,
+launch on the current stream."""
+import ctypes
+from ctypes import c_float, c_int, c_long, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc import build
+from .types import BatchMeta, PagedKV
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_EPI = {"store": 0, "add": 1, "swiglu": 2}
+_PAIRING = {"interleaved": 0, "half": 1}
+
+
+def _fail(msg):
+    from . import KernelError
+    raise KernelError(msg)
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype not in _DT:
+        _fail(f"kernels take float32 or bfloat16, got {t.dtype}")
+    return _DT[t.dtype]
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, dtype=None, shape=None, name="tensor"):
+    if not t.is_cuda:
+        _fail(f"{name} is on {t.device}: the kernels of this library run on a CUDA device only")
+    if not t.is_contiguous():
+        _fail(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        _fail(f"{name} must be {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        _fail(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class CudaKernels:
+    """The operations of `ops`, bound to the sm_100a libraries.  A library is
+    compiled and loaded when its first function is needed."""
+
+    def __init__(self):
+        if not torch.cuda.is_available():
+            _fail("no CUDA device: this library has no CPU path")
+        self._fn = {}
+
+    def _f(self, lib: str, name: str):
+        key = (lib, name)
+        fn = self._fn.get(key)
+        if fn is None:
+            handle = build.library(lib)
+            fn = getattr(handle, name)
+            fn.restype = c_int
+            self._fn[key] = fn
+            fn._lib = handle
+        return fn
+
+    def _call(self, lib, name, *args):
+        fn = self._f(lib, name)
+        if fn(*args) != 0:
+            _fail(f"{name}: {fn._lib.gfb_last_error().decode()}")
+
+    # -- element-wise / per-row -------------------------------------------------
+    def embed(self, tokens, table, out, status):
+        T = tokens.shape[0]
+        V, D = table.shape
+        _need(tokens, torch.int32, name="tokens")
+        _need(table, name="embedding table")
+        _need(out, torch.float32, (T, D), "embedding output")
+        self._call("core", "gfb_embed", _ptr(tokens), _ptr(table), c_int(_dt(table)), _ptr(out),
+                   c_int(T), c_int(D), c_int(V), _ptr(status), _stream())
+
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        D = x.shape[-1]
+        R = out.shape[0]
+        _need(x, torch.float32, name="norm input")
+        _need(weight, shape=(D,), name="norm weight")
+        _need(out, shape=(R, D), name="norm output")
+        if rows is not None:
+            _need(rows, torch.int32, (R,), "rows")
+        elif x.shape[0] != R:
+            _fail(f"norm output has {R} rows, input {x.shape[0]}")
+        self._call("core", "gfb_rmsnorm", _ptr(x), _ptr(weight), c_int(_dt(weight)), _ptr(out), c_int(_dt(out)),
+                   _ptr(rows), c_int(R), c_int(D), c_float(eps), _stream())
+
+    def rope_table(self, inv_freq, table):
+        P, half, two = table.shape
+        _need(inv_freq, torch.float32, (half,), "inv_freq")
+        _need(table, torch.float32, name="rotary table")
+        self._call("core", "gfb_rope_table", _ptr(inv_freq), _ptr(table), c_int(P), c_int(half), _stream())
+
+    def _batch_args(self, b: BatchMeta):
+        return (_ptr(b.cu_seqlens), _ptr(b.tok_seq), _ptr(b.slots), _ptr(b.lengths), c_int(b.n_seqs), c_int(b.n_tokens))
+
+    def _kv_args(self, kv: PagedKV):
+        return (_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.page_table), c_int(kv.page_table.shape[1]),
+                c_int(kv.page_size), c_int(kv.k_pool.shape[0]))
+
+    def rope_append(self, qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing, append):
+        T = batch.n_tokens
+        _need(qkv, shape=(T, (n_head + 2 * n_kv) * head_dim), name="qkv")
+        _need(q_out, qkv.dtype, (T, n_head, head_dim), "q_out")
+        _need(table, torch.float32, name="rotary table")
+        if append:
+            _need(kv.k_pool, qkv.dtype, name="key pool")
+            if tuple(kv.k_pool.shape[1:]) != (n_kv, kv.page_size, head_dim):
+                _fail(f"key pool pages are {tuple(kv.k_pool.shape[1:])}, the layer needs {(n_kv, kv.page_size, head_dim)}")
+        self._call("core", "gfb_rope_append", _ptr(qkv), _ptr(q_out), c_int(_dt(qkv)), *self._kv_args(kv),
+                   *self._batch_args(batch), _ptr(table), c_int(table.shape[0]), c_int(n_head), c_int(n_kv),
+                   c_int(head_dim), c_int(_PAIRING[pairing]), c_int(1 if append else 0), _ptr(batch.status), _stream())
+
+    def advance_lengths(self, batch):
+        self._call("core", "gfb_advance_lengths", _ptr(batch.lengths), _ptr(batch.slots), _ptr(batch.cu_seqlens),
+                   c_int(batch.n_seqs), _stream())
+
+    def add_into(self, out, y):
+        _need(out, torch.float32, name="sum")
+        _need(y, shape=out.shape, name="addend")
+        self._call("core", "gfb_add_into", _ptr(out), _ptr(y), c_int(_dt(y)), c_long(out.numel()), _stream())
+
+    # -- matrix products -----------------------------------------------------------
+    def linear(self, a, w, out, mode="store"):
+        M, K = a.shape
+        N = w.shape[0]
+        _need(a, name="activation")
+        _need(w, a.dtype, (N, K), "weight")
+        No = N // 2 if mode == "swiglu" else N
+        _need(out, shape=(M, No), name="product output")
+        if mode == "add" and out.dtype != torch.float32:
+            _fail("the residual sum is kept in float32")
+        if mode != "add" and out.dtype not in (a.dtype, torch.float32):
+            _fail(f"product of {a.dtype} cannot be stored as {out.dtype}")
+        if a.dtype == torch.bfloat16 and self._tc_fits(M, N, K, mode):
+            return self._linear_tc(a, w, out, mode)
+        if a.dtype == torch.float32 and out.dtype != torch.float32:
+            _fail("a float32 product is stored as float32")
+        self._call("gemm_simt", "gfb_gemm_simt", _ptr(a), _ptr(w), _ptr(out), c_int(_dt(a)), c_int(_dt(out)),
+                   c_int(M), c_int(N), c_int(K), c_int(_EPI[mode]), _stream())
+
+    def _tc_fits(self, M, N, K, mode) -> bool:
+        return False
+
+    def _linear_tc(self, a, w, out, mode):
+        raise NotImplementedError
+
+    # -- attention ---------------------------------------------------------------------
+    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None):
+        T = batch.n_tokens
+        _need(q, shape=(T, n_head, head_dim), name="q")
+        _need(out, q.dtype, (T, n_head * head_dim), "attention output")
+        _need(kv.k_pool, q.dtype, name="key pool")
+        self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
+                   *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim),
+                   c_float(scale), c_int(window or 0), _ptr(batch.status), _stream())
+
+    # -- sampling --------------------------------------------------------------------------
+    def argmax(self, logits, out):
+        B, V = logits.shape
+        _need(logits, torch.float32, name="logits")
+        _need(out, torch.int32, (B,), "token output")
+        self._call("sampling", "gfb_argmax", _ptr(logits), _ptr(out), c_int(B), c_int(V), _stream())
+
+    def sample(self, logits, out, temperature, top_k, seed, request_ids=None, token_index=None, index_map=None,
+               noise_out=None):
+        B, V = logits.shape
+        _need(logits, torch.float32, name="logits")
+        _need(out, torch.int32, (B,), "token output")
+        if request_ids is not None:
+            _need(request_ids, torch.int64, (B,), "request ids")
+        if token_index is not None:
+            _need(token_index, torch.int32, name="token index")
+        if index_map is not None:
+            _need(index_map, torch.int32, (B,), "index map")
+        elif token_index is not None and token_index.shape[0] < B:
+            _fail("token index has fewer entries than logits has rows")
+        if noise_out is not None:
+            _need(noise_out, torch.float32, (B, V), "noise output")
+        self._call("sampling", "gfb_sample", _ptr(logits), _ptr(out), c_int(B), c_int(V), c_float(temperature),
+                   c_int(int(top_k) if top_k else 0), c_ulonglong(seed & (2 ** 64 - 1)), _ptr(request_ids),
+                   _ptr(token_index), _ptr(index_map), _ptr(noise_out), _stream())

@@ -1,0 +1,58 @@
+"""Registries of the parts a layer is made of.
+
+A part is a small class that owns its parameters and launches kernels through
+`ops`; it takes its sizes and constants as constructor arguments and never
+sees the model's configuration.  Five kinds, one registry each:
+
+    NORMS          forward(x32 [T,D], out [R,D], rows=None)
+    POSITIONS      prepare(max_positions, device); what a mixer needs to place tokens
+    MIXERS         cache_needs(); forward(h, batch, view, residual, append)
+    FEED_FORWARDS  forward(h, residual)
+    BLOCKS         forward(x32, batch, view, append): the arrangement of the above
+
+Every part also has `param_specs()` (name -> weights.loader.ParamSpec) and
+`load(tensors)`.  Mixers and feed-forwards ADD their result into `residual`
+(float32, in place): the residual sum is part of the producing kernel where
+that is possible, `ops.add_into` otherwise.
+
+`register_*` adds a class under a name; a `config.spec.PartSpec` names it.
+"""
+from typing import Any, Callable, Dict
+
+from ..config.spec import PartSpec
+
+NORMS: Dict[str, Callable] = {}
+POSITIONS: Dict[str, Callable] = {}
+MIXERS: Dict[str, Callable] = {}
+FEED_FORWARDS: Dict[str, Callable] = {}
+BLOCKS: Dict[str, Callable] = {}
+
+
+def _registrar(table: Dict[str, Callable], kind: str):
+    def register(name: str, factory: Callable = None):
+        """`register(name, cls)` or `@register(name)` above a class."""
+        def put(f):
+            if name in table and table[name] is not f:
+                raise ValueError(f"{kind} '{name}' is already registered")
+            table[name] = f
+            return f
+        return put(factory) if factory is not None else put
+    return register
+
+
+register_norm = _registrar(NORMS, "norm")
+register_position = _registrar(POSITIONS, "position encoding")
+register_mixer = _registrar(MIXERS, "mixer")
+register_feed_forward = _registrar(FEED_FORWARDS, "feed-forward")
+register_block = _registrar(BLOCKS, "block")
+
+
+def build_part(table: Dict[str, Callable], spec: PartSpec, **extra: Any):
+    """Construct the part that `spec` names, with the spec's parameters plus
+    what the model adds (dtype, a position encoding, ...)."""
+    if spec.kind not in table:
+        raise KeyError(f"no part named '{spec.kind}' is registered; known: {sorted(table)}")
+    return table[spec.kind](**spec.params, **extra)
+
+
+from . import norm, rope, attention, feed_forward, block  # noqa: E402,F401  (register the built-in parts)

@@ -1,0 +1,54 @@
+"""Causal grouped-query attention with a fused q/k/v projection
+(gpt-fast model.py:167-216).
+
+Steps: qkv = h Wqkv^T; rotate q and k by each token's position and append k, v
+to the sequence's place in the cache (one kernel); attention of the new
+queries over the cache; residual += y Wo^T.  Query head h reads key/value
+head h // (n_head / n_kv); the scale is 1/sqrt(head_dim) unless given."""
+import math
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..cache.needs import CacheNeeds, KVNeed
+from ..weights.loader import ParamSpec
+from . import register_mixer
+
+
+@register_mixer("attention")
+class Attention:
+    def __init__(self, dim: int, n_head: int, n_kv: int, head_dim: int, dtype: torch.dtype, position,
+                 window: Optional[int] = None, scale: Optional[float] = None):
+        if n_head % n_kv:
+            raise ValueError(f"{n_head} query heads do not divide into {n_kv} key/value heads")
+        if position is None:
+            raise ValueError("attention needs a position encoding")
+        self.dim, self.n_head, self.n_kv, self.head_dim = dim, n_head, n_kv, head_dim
+        self.window, self.dtype, self.position = window, dtype, position
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.wqkv = self.wo = None
+
+    def param_specs(self):
+        H, G, d, D = self.n_head, self.n_kv, self.head_dim, self.dim
+        return {"wq": ParamSpec((H * d, D)), "wk": ParamSpec((G * d, D)), "wv": ParamSpec((G * d, D)),
+                "wo": ParamSpec((D, H * d))}
+
+    def load(self, tensors):
+        # rows: q heads, then k heads, then v heads (gpt-fast model.py:184-189)
+        self.wqkv = torch.cat([tensors["wq"], tensors["wk"], tensors["wv"]]).contiguous()
+        self.wo = tensors["wo"]
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(kv=KVNeed(self.n_kv, self.head_dim, self.window))
+
+    def forward(self, h, batch, view, residual, append: bool = True):
+        T = batch.n_tokens
+        H, G, d = self.n_head, self.n_kv, self.head_dim
+        qkv = torch.empty(T, (H + 2 * G) * d, dtype=self.dtype, device=h.device)
+        ops.linear(h, self.wqkv, qkv)
+        q = torch.empty(T, H, d, dtype=self.dtype, device=h.device)
+        ops.rope_append(qkv, q, view.kv, batch, self.position.table, H, G, d, self.position.pairing, append)
+        y = torch.empty(T, H * d, dtype=self.dtype, device=h.device)
+        ops.attention(q, view.kv, batch, y, H, G, d, self.scale, self.window)
+        ops.linear(y, self.wo, residual, mode="add")
