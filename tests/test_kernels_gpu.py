@@ -37,7 +37,7 @@ def make_batch(q_lens, starts, n_slots, page_size, max_pages, seed=0):
     perm = torch.randperm(n_pages, generator=g).tolist()
     for i, s in enumerate(slots):
         lengths[s] = starts[i]
-        for j in range(need[i]):
+        for j in range(min(need[i], max_pages)):
             table[s, j] = perm.pop()
     cu = [0]
     for q in q_lens:
