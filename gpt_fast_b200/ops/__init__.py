@@ -53,6 +53,9 @@ def new_status(device) -> torch.Tensor:
 def check_status(status: torch.Tensor) -> None:
     """Read the device-side error words (this synchronises) and raise if a
     kernel reported something; the words are cleared afterwards."""
+    own = getattr(_kernels, "_status", None)
+    if own is not None and own is not status:
+        check_status(own)
     s = status.tolist()
     if s[0] != 0:
         status.zero_()

@@ -52,6 +52,8 @@ class CudaKernels:
         if not torch.cuda.is_available():
             _fail("no CUDA device: this library has no CPU path")
         self._fn = {}
+        self._sm_count = None
+        self._status = None
 
     def _f(self, lib: str, name: str):
         key = (lib, name)
@@ -147,10 +149,45 @@ class CudaKernels:
                    c_int(M), c_int(N), c_int(K), c_int(_EPI[mode]), _stream())
 
     def _tc_fits(self, M, N, K, mode) -> bool:
-        return False
+        """The tensor-core kernel takes rows of whole 16-byte units (TMA) and stores in 16-byte vectors."""
+        return K % 8 == 0 and N % (16 if mode == "swiglu" else 8) == 0
 
-    def _linear_tc(self, a, w, out, mode):
-        raise NotImplementedError
+    def tc_plan(self, M, N, K):
+        """(swap, bn, splits, stages) for the tensor-core product.  Few tokens: the weight rows fill the
+        128 MMA rows and the tokens are its columns, split over K until about two blocks per SM stream
+        weights; many tokens: 128 tokens x 256 weight rows per block."""
+        if M <= 128:
+            bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+            blocks = -(-N // 128)
+            total_kb = -(-K // 64)
+            splits = max(1, min(total_kb // 8, (2 * self.sm_count) // blocks))
+            stage = 16384 + bn * 128
+            stages = max(2, min(8, (100 * 1024) // stage))
+            return 1, bn, splits, stages
+        bn = 256 if N >= 256 else 128
+        return 0, bn, 1, 4 if bn == 256 else 6
+
+    @property
+    def sm_count(self):
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        return self._sm_count
+
+    @property
+    def status(self):
+        """Error words of kernels that take no status of a step (bounded waits that ran out)."""
+        if self._status is None:
+            self._status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        return self._status
+
+    def _linear_tc(self, a, w, out, mode, plan=None):
+        M, K = a.shape
+        N = w.shape[0]
+        swap, bn, splits, stages = plan or self.tc_plan(M, N, K)
+        ws = torch.empty(splits, M, N, dtype=torch.float32, device=a.device) if splits > 1 else None
+        self._call("gemm_tc", "gfb_gemm_tc", _ptr(a), _ptr(w), _ptr(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
+                   c_int(_EPI[mode]), c_int(swap), c_int(bn), c_int(splits), c_int(stages), _ptr(ws),
+                   _ptr(self.status), _stream())
 
     # -- attention ---------------------------------------------------------------------
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None):

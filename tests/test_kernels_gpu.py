@@ -295,3 +295,56 @@ def test_sample_frequencies_follow_softmax():
     freq = torch.bincount(out.long().cpu(), minlength=V).float() / 4000
     p = torch.softmax(logits[0].cpu(), -1)
     assert (freq - p).abs().max() < 0.03
+
+
+# ---- tensor-core product (tcgen05 + TMA) -------------------------------------------------
+TC_SHAPES = [(1, 384, 144), (8, 512, 256), (5, 320, 144), (16, 1024, 4096), (17, 6144, 512), (64, 768, 2048),
+             (100, 1008, 200), (128, 256, 64), (129, 512, 1024), (300, 640, 456), (256, 2048, 4096)]
+
+
+@pytest.mark.parametrize("mode", ["store", "store32", "add", "swiglu"])
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_linear_tensor_core(mode, M, N, K):
+    a = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    k = ops.kernels()
+    m = "store" if mode == "store32" else mode
+    assert k._tc_fits(M, N, K, m)
+    if mode == "add":
+        out = rnd(M, N, seed=2)
+        ref = out.clone()
+    else:
+        No = N // 2 if mode == "swiglu" else N
+        out = torch.empty(M, No, dtype=torch.float32 if mode == "store32" else torch.bfloat16, device=DEV)
+        ref = torch.empty_like(out)
+    ops.linear(a, w, out, m)
+    REF.linear(a, w, ref, m)
+    ops.check_status(ops.new_status(DEV))
+    if out.dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
+    else:
+        torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("swap,bn,splits,stages", [(1, 16, 1, 2), (1, 16, 3, 6), (1, 32, 2, 4), (1, 64, 5, 3), (1, 128, 1, 4),
+                                                   (1, 128, 4, 3), (0, 128, 1, 2), (0, 128, 1, 6), (0, 256, 1, 4), (0, 256, 1, 3)])
+@pytest.mark.parametrize("mode", ["store", "add", "swiglu"])
+def test_tensor_core_plans(swap, bn, splits, stages, mode):
+    """Every orientation, tile width, split and ring depth gives the same product."""
+    M, N, K = (bn if swap else 150), 800, 1160
+    M = min(M, 70) if bn >= 64 and swap else M
+    a = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    if mode == "add":
+        out = rnd(M, N, seed=2)
+        ref = out.clone()
+    else:
+        out = torch.empty(M, N // 2 if mode == "swiglu" else N, dtype=torch.bfloat16, device=DEV)
+        ref = torch.empty_like(out)
+    ops.kernels()._linear_tc(a, w, out, mode, plan=(swap, bn, splits, stages))
+    REF.linear(a, w, ref, mode)
+    ops.check_status(ops.new_status(DEV))
+    if mode == "add":
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
+    else:
+        torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
