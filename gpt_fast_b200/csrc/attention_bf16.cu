@@ -1,0 +1,261 @@
+// bfloat16 attention kernels of the serving path (the 32-bit path and odd
+// sizes use attention_generic.cu).  They stand where gpt-fast expands K/V to all
+// heads and calls SDPA over the whole cache (model.py:209-211).
+//
+// attn_decode: one new token per sequence.  A block owns (sequence, key/value
+// head, slice of the sequence's pages) and serves all query heads of the group
+// from one pass over the keys and values, so each cached byte is read once per
+// group, not once per head.  Pages (64 tokens x head_dim, contiguous per head)
+// are brought to shared memory with cp.async, double buffered.  Scores,
+// softmax and the weighted sum are 32-bit.  With more than one slice per
+// sequence the blocks write (max, sum, unnormalised output) to scratch and
+// attn_combine merges the slices in ascending order.
+#include "common.cuh"
+
+GFB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int PAGE = 64;
+constexpr int THREADS = 128;
+constexpr int MAX_REP = 8;          // query heads per key/value head
+constexpr int MAX_DPT = 2;          // head_dim <= THREADS * MAX_DPT
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// q: [T, H, d]; out: [T, H*d]; scratch_o: [T, H, S, d] f32; scratch_ml: [T, H, S, 2] f32
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                   float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
+                   GfbPagedKV kv, GfbBatch b, int H, int G, int d, float scale_log2e, int window, int splits, int* status) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int rep = H / G;
+    const int tile_bytes = PAGE * d * 2;
+    __nv_bfloat16* kbuf[2] = {(__nv_bfloat16*)smem, (__nv_bfloat16*)(smem + 2 * tile_bytes)};
+    __nv_bfloat16* vbuf[2] = {(__nv_bfloat16*)(smem + tile_bytes), (__nv_bfloat16*)(smem + 3 * tile_bytes)};
+    float* qs = (float*)(smem + 4 * tile_bytes);          // [rep][d], pre-scaled
+    float* ps = qs + rep * d;                             // [rep][PAGE]
+    __shared__ float red[MAX_REP][2];      // per head: (rescale of what was summed so far, sum of this tile)
+    __shared__ float mrun[MAX_REP];        // per head: running maximum
+
+    const int t = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
+    const int s = b.tok_seq[t];
+    const int slot = b.slots[s];
+    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_page = lo / PAGE, last_page = pos / PAGE;
+    const int n_pages = last_page - first_page + 1;
+    const int per = (n_pages + splits - 1) / splits;
+    const int p0 = first_page + z * per;
+    const int p1 = min(last_page + 1, p0 + per);
+    const int tid = threadIdx.x;
+
+    for (int i = tid; i < rep * d; i += THREADS) {
+        int h = i / d;
+        qs[i] = __bfloat162float(q[((size_t)t * H + g * rep + h) * d + (i - h * d)]) * scale_log2e;
+    }
+
+    if (tid < MAX_REP) mrun[tid] = -INFINITY;
+    float l_run[MAX_REP], acc[MAX_REP][MAX_DPT];
+#pragma unroll
+    for (int h = 0; h < MAX_REP; h++) {
+        l_run[h] = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) acc[h][r] = 0.f;
+    }
+
+    const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
+    const int chunks = tile_bytes / 16;                   // 16-byte pieces of one tile
+    auto issue = [&](int page_index, int buf) {
+        int page = pt[page_index];
+        if (page < 0 || page >= kv.n_pages) {
+            if (tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, page_index);
+            page = 0;                                     // read a valid page; its scores are masked below
+        }
+        const uint8_t* ksrc = (const uint8_t*)kv.k_pool + ((size_t)page * G + g) * tile_bytes;
+        const uint8_t* vsrc = (const uint8_t*)kv.v_pool + ((size_t)page * G + g) * tile_bytes;
+        for (int c = tid; c < chunks; c += THREADS) {
+            cp_async16((uint8_t*)kbuf[buf] + c * 16, ksrc + c * 16);
+            cp_async16((uint8_t*)vbuf[buf] + c * 16, vsrc + c * 16);
+        }
+    };
+
+    if (p0 < p1) issue(p0, 0);
+    cp_async_commit();
+    const int key = tid & (PAGE - 1), hg = tid >> 6;      // QK: 64 keys x 2 head groups
+    const int d8 = d >> 3;
+    for (int p = p0; p < p1; p++) {
+        const int buf = (p - p0) & 1;
+        if (p + 1 < p1) issue(p + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();                                  // tile p landed; qs ready (first pass)
+
+        // scores of this thread's key for heads hg, hg+2, ...
+        const int j = p * PAGE + key;
+        const bool live = j >= lo && j <= pos;
+        float dot[MAX_REP / 2];
+#pragma unroll
+        for (int i = 0; i < MAX_REP / 2; i++) dot[i] = 0.f;
+        const uint4* krow = reinterpret_cast<const uint4*>(kbuf[buf] + (size_t)key * d);
+        const int start = key % d8;                       // rotate the start: neighbouring keys hit different banks
+        for (int c = 0; c < d8; c++) {
+            int cc = start + c;
+            if (cc >= d8) cc -= d8;
+            uint4 raw = krow[cc];
+            const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float kf[8];
+#pragma unroll
+            for (int e = 0; e < 4; e++) { float2 f = __bfloat1622float2(k2[e]); kf[2 * e] = f.x; kf[2 * e + 1] = f.y; }
+#pragma unroll
+            for (int i = 0; i < MAX_REP / 2; i++) {
+                int h = hg + 2 * i;
+                if (h < rep) {
+                    const float4* qv = reinterpret_cast<const float4*>(qs + h * d + cc * 8);
+                    float4 a = qv[0], c4 = qv[1];
+                    dot[i] += a.x * kf[0] + a.y * kf[1] + a.z * kf[2] + a.w * kf[3]
+                            + c4.x * kf[4] + c4.y * kf[5] + c4.z * kf[6] + c4.w * kf[7];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_REP / 2; i++) {
+            int h = hg + 2 * i;
+            if (h < rep) ps[h * PAGE + key] = live ? dot[i] : -INFINITY;
+        }
+        __syncthreads();
+
+        // per head: tile max and probabilities (warp w serves heads w, w+4)
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int h = warp; h < rep; h += THREADS / 32) {
+            float s0 = ps[h * PAGE + lane], s1 = ps[h * PAGE + 32 + lane];
+            float mx = gfb_warp_max(fmaxf(s0, s1));
+            float m_old = mrun[h];
+            float m_new = fmaxf(m_old, mx);
+            float e0 = (s0 == -INFINITY) ? 0.f : exp2f(s0 - m_new);
+            float e1 = (s1 == -INFINITY) ? 0.f : exp2f(s1 - m_new);
+            ps[h * PAGE + lane] = e0;
+            ps[h * PAGE + 32 + lane] = e1;
+            float sum = gfb_warp_sum(e0 + e1);
+            if (lane == 0) {
+                red[h][0] = (m_old == -INFINITY) ? 0.f : exp2f(m_old - m_new);
+                red[h][1] = sum;
+                mrun[h] = m_new;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < MAX_REP; h++) {
+            if (h < rep) {
+                float corr = red[h][0];
+                l_run[h] = l_run[h] * corr + red[h][1];
+#pragma unroll
+                for (int r = 0; r < MAX_DPT; r++) acc[h][r] *= corr;
+            }
+        }
+        // weighted sum: thread owns dims tid, tid + 128
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) {
+            int dim = tid + r * THREADS;
+            if (dim < d) {
+                const __nv_bfloat16* vcol = vbuf[buf] + dim;
+                for (int jj = 0; jj < PAGE; jj++) {
+                    float v = __bfloat162float(vcol[(size_t)jj * d]);
+#pragma unroll
+                    for (int h = 0; h < MAX_REP; h++)
+                        if (h < rep) acc[h][r] = fmaf(ps[h * PAGE + jj], v, acc[h][r]);
+                }
+            }
+        }
+        __syncthreads();                                  // ps and this buffer are reused next round
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                      // mrun is final (also when this block had no page)
+
+#pragma unroll
+    for (int h = 0; h < MAX_REP; h++) {
+        if (h >= rep) continue;
+        const int head = g * rep + h;
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) {
+            int dim = tid + r * THREADS;
+            if (dim >= d) continue;
+            if (splits == 1) {
+                float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+                out[((size_t)t * H + head) * d + dim] = __float2bfloat16_rn(acc[h][r] * inv);
+            } else {
+                scratch_o[(((size_t)t * H + head) * splits + z) * d + dim] = acc[h][r];
+            }
+        }
+        if (splits > 1 && tid == 0) {
+            float* ml = scratch_ml + (((size_t)t * H + head) * splits + z) * 2;
+            ml[0] = mrun[h];
+            ml[1] = l_run[h];
+        }
+    }
+}
+
+__global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
+                                    __nv_bfloat16* __restrict__ out, int H, int d, int splits) {
+    const int t = blockIdx.x, head = blockIdx.y;
+    const float* ml = scratch_ml + ((size_t)t * H + head) * splits * 2;
+    float m = -INFINITY;
+    for (int z = 0; z < splits; z++) m = fmaxf(m, ml[2 * z]);
+    float l = 0.f;
+    for (int z = 0; z < splits; z++) l += (ml[2 * z] == -INFINITY) ? 0.f : ml[2 * z + 1] * exp2f(ml[2 * z] - m);
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+        float o = 0.f;
+        for (int z = 0; z < splits; z++) {
+            if (ml[2 * z] == -INFINITY) continue;
+            o += scratch_o[(((size_t)t * H + head) * splits + z) * d + dim] * exp2f(ml[2 * z] - m);
+        }
+        out[((size_t)t * H + head) * d + dim] = __float2bfloat16_rn(o * inv);
+    }
+}
+
+}  // namespace
+
+// Bytes of scratch the decode kernel needs for `splits` > 1: [T, H, splits, d + 2] floats.
+GFB_API long gfb_attn_decode_scratch_bytes(int T, int H, int d, int splits) {
+    return splits > 1 ? (long)T * H * splits * (d + 2) * 4 : 0;
+}
+
+GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                            int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                            const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                            int splits, float* scratch, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (page_size != PAGE) return gfb_fail("gfb_attn_decode: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
+    if (d % 8 || d > THREADS * MAX_DPT) return gfb_fail("gfb_attn_decode: head_dim %d must be a multiple of 8, at most %d", d, THREADS * MAX_DPT);
+    if (G <= 0 || H % G || H / G > MAX_REP) return gfb_fail("gfb_attn_decode: %d heads over %d groups (at most %d per group)", H, G, MAX_REP);
+    if (splits < 1 || G > 65535 || splits > 65535) return gfb_fail("gfb_attn_decode: bad split count %d", splits);
+    if (splits > 1 && scratch == nullptr) return gfb_fail("gfb_attn_decode: %d slices need scratch memory", splits);
+    const int rep = H / G;
+    size_t smem = (size_t)4 * PAGE * d * 2 + (size_t)rep * d * 4 + (size_t)rep * PAGE * 4;
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gfb_fail("gfb_attn_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = smem;
+    }
+    GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
+    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    float* so = scratch;
+    float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
+    dim3 grid(n_tokens, G, splits);
+    attn_decode_kernel<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b, H, G, d,
+                                                        scale * 1.4426950408889634f, window, splits, status);
+    if (gfb_check_launch("gfb_attn_decode")) return 1;
+    if (splits > 1) {
+        dim3 cgrid(n_tokens, H);
+        attn_combine_kernel<<<cgrid, 128, 0, stream>>>(so, sml, (__nv_bfloat16*)out, H, d, splits);
+        return gfb_check_launch("gfb_attn_decode (combine)");
+    }
+    return 0;
+}

@@ -195,9 +195,26 @@ class CudaKernels:
         _need(q, shape=(T, n_head, head_dim), name="q")
         _need(out, q.dtype, (T, n_head * head_dim), "attention output")
         _need(kv.k_pool, q.dtype, name="key pool")
+        if (q.dtype == torch.bfloat16 and kv.page_size == 64 and head_dim % 8 == 0 and head_dim <= 256
+                and n_head // n_kv <= 8):
+            return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim),
                    c_float(scale), c_int(window or 0), _ptr(batch.status), _stream())
+
+    def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None):
+        T = batch.n_tokens
+        if splits is None:
+            splits = 1
+            if batch.max_q_len == 1:       # decode: slice long sequences until about two blocks per SM work
+                pages = -(-max(batch.max_kv_len, 1) // kv.page_size)
+                splits = max(1, min(pages, 32, (2 * self.sm_count) // max(1, T * n_kv)))
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(T * n_head * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+        self._call("attention_bf16", "gfb_attn_decode", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                   c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(splits),
+                   _ptr(scratch), _ptr(batch.status), _stream())
 
     # -- sampling --------------------------------------------------------------------------
     def argmax(self, logits, out):

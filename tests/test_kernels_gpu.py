@@ -348,3 +348,30 @@ def test_tensor_core_plans(swap, bn, splits, stages, mode):
         torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
     else:
         torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+# ---- bfloat16 attention over the paged cache ------------------------------------------------
+BF16_ATTN_CASES = [  # H, G, d, q_lens, starts
+    (4, 4, 16, [1, 1, 1], [4, 63, 64]),
+    (6, 2, 24, [1, 1, 1, 1], [0, 6, 129, 700]),
+    (32, 8, 128, [1, 1], [127, 1500]),
+    (8, 1, 64, [1, 1, 1], [300, 65, 2]),
+    (6, 2, 48, [5, 1, 70], [0, 200, 30]),          # also correct (if not fast) for longer runs of new tokens
+    (5, 5, 256, [1, 3], [90, 10]),
+]
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("H,G,d,q_lens,starts", BF16_ATTN_CASES)
+def test_attention_bf16_decode(splits, window, H, G, d, q_lens, starts):
+    batch, table, n_pages = make_batch(q_lens, starts, 9, 64, 32, seed=3)
+    T = batch.n_tokens
+    dt = torch.bfloat16
+    kv = PagedKV(rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5), table, 64)
+    q = rnd(T, H, d, dtype=dt, seed=6)
+    out, ref = torch.empty(T, H * d, dtype=dt, device=DEV), torch.empty(T, H * d, dtype=dt, device=DEV)
+    ops.kernels()._attention_bf16(q, kv, batch, out, H, G, d, 1 / math.sqrt(d), window, splits=splits)
+    REF.attention(q, kv, batch, ref, H, G, d, 1 / math.sqrt(d), window)
+    ops.check_status(batch.status)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
