@@ -259,3 +259,45 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     }
     return 0;
 }
+
+// ---- the entry point that allocates nothing (see attn_decode_noalloc.h) -----------------
+#include "attn_decode_noalloc.h"
+
+// Scratch of the split-KV partials for callers that cannot allocate.  In host code this name is
+// only a handle for the runtime, not a device address: its address is looked up once per device.
+static __device__ __align__(256) float gfb_noalloc_scratch[GFB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}
+
+GFB_API int gfb_attn_decode_noalloc(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table,
+                                    int max_pages, int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq,
+                                    const int* slots, const int* lengths, int n_seqs, int n_tokens, int H, int G, int d,
+                                    float scale, int window, int splits, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (splits < 1 || H <= 0 || d <= 0) return gfb_fail("gfb_attn_decode_noalloc: bad sizes (H %d, d %d, splits %d)", H, d, splits);
+    float* scratch = nullptr;
+    if (splits > 1) {
+        long long need = (long long)n_tokens * H * splits * (d + 2);
+        if (need > (long long)GFB_NOALLOC_SCRATCH_FLOATS)
+            return gfb_fail("gfb_attn_decode_noalloc: %d tokens x %d heads x %d slices x (%d + 2) = %lld floats of scratch "
+                            "exceed the built-in %d; use fewer slices or gfb_attn_decode with your own scratch",
+                            n_tokens, H, splits, d, need, GFB_NOALLOC_SCRATCH_FLOATS);
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return gfb_fail("gfb_attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+        if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return gfb_fail("gfb_attn_decode_noalloc: device %d out of range", dev);
+        if (noalloc_scratch_ptr[dev] == nullptr) {          // set-up, once per device, with that device current
+            float* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, gfb_noalloc_scratch);
+            if (e != cudaSuccess || p == nullptr)
+                return gfb_fail("gfb_attn_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            noalloc_scratch_ptr[dev] = p;
+        }
+        scratch = noalloc_scratch_ptr[dev];
+    }
+    return gfb_attn_decode(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
+                           lengths, n_seqs, n_tokens, H, G, d, scale, window, splits, scratch, status, stream);
+}

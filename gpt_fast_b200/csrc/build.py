@@ -31,7 +31,7 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], [], ["cuda"]),
     "attention_bf16": (["attention_bf16.cu"], [], []),
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attn_decode_noalloc.h"]
 
 _loaded = {}
 _lock = threading.Lock()
