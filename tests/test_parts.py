@@ -1,0 +1,238 @@
+"""Each part of a layer alone against the plain implementation, and a toy mixer
+with state of its own that is registered, built and stepped without a change to
+the library's files."""
+import math
+
+import pytest
+import torch
+
+import gpt_fast_b200 as gf
+from gpt_fast_b200 import ops, parts
+from gpt_fast_b200.cache import Cache, CacheNeeds, StateNeed
+from gpt_fast_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from gpt_fast_b200.engine.model import Transformer
+from gpt_fast_b200.ops.types import BatchMeta
+from gpt_fast_b200.weights.loader import ParamSpec
+import plain_llama
+import plain_ops
+
+BACKENDS = [
+    pytest.param(("cpu", torch.float32), id="cpu-standin-f32"),
+    pytest.param(("cuda", torch.float32), id="cuda-f32", marks=pytest.mark.gpu),
+    pytest.param(("cuda", torch.bfloat16), id="cuda-bf16", marks=pytest.mark.gpu),
+]
+
+
+@pytest.fixture(params=BACKENDS)
+def backend(request):
+    device, dtype = request.param
+    prev = ops.use_kernels(plain_ops.PlainOps()) if device == "cpu" else None
+    yield device, dtype
+    if device == "cpu":
+        ops.use_kernels(prev)
+
+
+def tol(dtype):
+    return dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+def rnd(*shape, scale=1.0, seed=0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def bf16_exact(t):
+    return t.bfloat16().float()
+
+
+def one_sequence_batch(cache, n_tokens, device):
+    slot = cache.begin(1)
+    cache.reserve(slot[0], n_tokens)
+    cache.sync_tables()
+    ar = torch.arange(n_tokens + 1, dtype=torch.int32)
+    return BatchMeta(torch.tensor([0, n_tokens], dtype=torch.int32).to(device),
+                     torch.zeros(n_tokens, dtype=torch.int32).to(device),
+                     torch.tensor(slot, dtype=torch.int32).to(device), cache.lengths, 1, n_tokens, n_tokens, n_tokens,
+                     ops.new_status(device))
+
+
+@pytest.mark.parametrize("dim,eps", [(64, 1e-5), (144, 1e-6), (200, 1e-2)])
+def test_rmsnorm_part(backend, dim, eps):
+    device, dtype = backend
+    norm = parts.build_part(parts.NORMS, PartSpec("rmsnorm", dict(dim=dim, eps=eps)), dtype=dtype)
+    assert norm.param_specs() == {"weight": ParamSpec((dim,), "vector")}
+    w = bf16_exact(1 + rnd(dim, scale=0.1, seed=1))
+    x = rnd(9, dim, scale=2.0)
+    norm.load({"weight": w.to(device)})
+    out = torch.empty(9, dim, dtype=dtype, device=device)
+    norm.forward(x.to(device), out)
+    torch.testing.assert_close(out.float().cpu(), plain_llama.rms_norm(x, w, eps), **tol(dtype))
+
+
+@pytest.mark.parametrize("head_dim,base,scaling", [
+    (16, 10000.0, None),
+    (24, 500000.0, dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=32)),
+    (128, 500000.0, dict(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)),
+])
+def test_rope_part(backend, head_dim, base, scaling):
+    device, _ = backend
+    rope = parts.build_part(parts.POSITIONS, PartSpec("rope", dict(head_dim=head_dim, base=base, scaling=scaling)))
+    freqs = plain_llama.rope_frequencies(head_dim, base, scaling)
+    assert torch.equal(rope.inv_freq, freqs)                       # the same 32-bit arithmetic as gpt-fast's
+    rope.prepare(300, device)
+    cos, sin = plain_llama.rope_angles(torch.arange(300), freqs)
+    torch.testing.assert_close(rope.table[..., 0].cpu(), cos, rtol=0, atol=3e-6)
+    torch.testing.assert_close(rope.table[..., 1].cpu(), sin, rtol=0, atol=3e-6)
+
+
+@pytest.mark.parametrize("dim,H,G,d,S", [(64, 4, 4, 16, 21), (144, 6, 2, 24, 70)])
+def test_attention_part(backend, dim, H, G, d, S):
+    device, dtype = backend
+    rope = parts.build_part(parts.POSITIONS, PartSpec("rope", dict(head_dim=d, base=10000.0)))
+    att = parts.build_part(parts.MIXERS, PartSpec("attention", dict(dim=dim, n_head=H, n_kv=G, head_dim=d)),
+                           dtype=dtype, position=rope)
+    ws = {"wq": bf16_exact(rnd(H * d, dim, scale=0.1, seed=1)), "wk": bf16_exact(rnd(G * d, dim, scale=0.1, seed=2)),
+          "wv": bf16_exact(rnd(G * d, dim, scale=0.1, seed=3)), "wo": bf16_exact(rnd(dim, H * d, scale=0.1, seed=4))}
+    assert {k: v.shape for k, v in att.param_specs().items()} == {k: tuple(v.shape) for k, v in ws.items()}
+    att.load({k: v.to(dtype).to(device) for k, v in ws.items()})
+    cache = Cache({0: att.cache_needs()}, dtype, device, max_tokens=128)
+    rope.prepare(128, device)
+    h = bf16_exact(rnd(S, dim, seed=5))
+    res0 = rnd(S, dim, seed=6)
+    residual = res0.clone().to(device)
+    batch = one_sequence_batch(cache, S, device)
+    att.forward(h.to(dtype).to(device), batch, cache.view(0), residual)
+    ops.check_status(batch.status)
+    cos, sin = plain_llama.rope_angles(torch.arange(S), plain_llama.rope_frequencies(d, 10000.0))
+    want = res0 + plain_llama.attention(h, torch.cat([ws["wq"], ws["wk"], ws["wv"]]), ws["wo"], cos, sin, H, G, d)
+    torch.testing.assert_close(residual.cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dim,hidden", [(64, 172), (144, 384)])
+def test_swiglu_part(backend, dim, hidden):
+    device, dtype = backend
+    ff = parts.build_part(parts.FEED_FORWARDS, PartSpec("swiglu", dict(dim=dim, hidden=hidden)), dtype=dtype)
+    ws = {"w1": bf16_exact(rnd(hidden, dim, scale=0.1, seed=1)), "w3": bf16_exact(rnd(hidden, dim, scale=0.1, seed=2)),
+          "w2": bf16_exact(rnd(dim, hidden, scale=0.1, seed=3))}
+    ff.load({k: v.to(dtype).to(device) for k, v in ws.items()})
+    h = bf16_exact(rnd(11, dim, seed=4))
+    res0 = rnd(11, dim, seed=5)
+    residual = res0.clone().to(device)
+    ff.forward(h.to(dtype).to(device), residual)
+    want = res0 + plain_llama.feed_forward(h, ws["w1"], ws["w2"], ws["w3"])
+    torch.testing.assert_close(residual.cpu(), want, **tol(dtype))
+
+
+# ---- a toy mixer with state of its own, defined here --------------------------------------------
+
+class RunningMeanMixer:
+    """y_t = (decay * s + h_t) W with s the previous such sum of the sequence: a
+    recurrent mixer whose only memory is a fixed-size state per sequence."""
+
+    def __init__(self, dim, decay, dtype, position=None):
+        self.dim, self.decay, self.dtype = dim, decay, dtype
+        self.w = None
+
+    def param_specs(self):
+        return {"w": ParamSpec((self.dim, self.dim))}
+
+    def load(self, tensors):
+        self.w = tensors["w"]
+
+    def cache_needs(self):
+        return CacheNeeds(state=StateNeed((self.dim,), torch.float32))
+
+    def forward(self, h, batch, view, residual, append=True):
+        cu = batch.cu_seqlens.tolist()
+        slots = batch.slots.tolist()
+        mixed = torch.empty(h.shape, dtype=torch.float32, device=h.device)
+        for i, slot in enumerate(slots):
+            s = view.state[slot].clone()
+            for t in range(cu[i], cu[i + 1]):
+                s = self.decay * s + h[t].float()
+                mixed[t] = s
+            if append:
+                view.state[slot] = s
+        y = (mixed @ self.w.float().T).to(self.dtype)
+        ops.add_into(residual, y)
+
+
+def toy_spec(dim=48, vocab=61):
+    norm = PartSpec("rmsnorm", dict(dim=dim, eps=1e-5))
+    rope = PartSpec("rope", dict(head_dim=12, base=10000.0))
+    ff = PartSpec("swiglu", dict(dim=dim, hidden=80))
+    toy = LayerSpec("prenorm", PartSpec("running_mean", dict(dim=dim, decay=0.5)), ff, norm, norm, None)
+    att = LayerSpec("prenorm", PartSpec("attention", dict(dim=dim, n_head=4, n_kv=2, head_dim=12)), ff, norm, norm, rope)
+    # layer 0 (toy) runs twice with the same weights and a state of its own each time
+    return ModelSpec("toy", dim, vocab, [toy, att],
+                     [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2)], norm, max_position=256)
+
+
+def toy_plain(tokens, P, spec):
+    """The toy model on one whole sequence with plain tensor code."""
+    x = P["embed.weight"].float()[tokens]
+    cos, sin = plain_llama.rope_angles(torch.arange(len(tokens)), plain_llama.rope_frequencies(12, 10000.0))
+    for e in spec.schedule:
+        pre = f"layers.{e.layer}."
+        h = plain_llama.rms_norm(x, P[pre + "mixer_norm.weight"].float(), 1e-5)
+        if e.layer == 0:
+            s, rows = torch.zeros(spec.dim), []
+            for t in range(len(tokens)):
+                s = 0.5 * s + h[t]
+                rows.append(s)
+            x = x + torch.stack(rows) @ P[pre + "mixer.w"].float().T
+        else:
+            wqkv = torch.cat([P[pre + "mixer.wq"], P[pre + "mixer.wk"], P[pre + "mixer.wv"]]).float()
+            x = x + plain_llama.attention(h, wqkv, P[pre + "mixer.wo"].float(), cos, sin, 4, 2, 12)
+        f = plain_llama.rms_norm(x, P[pre + "ffn_norm.weight"].float(), 1e-5)
+        x = x + plain_llama.feed_forward(f, P[pre + "feed_forward.w1"].float(), P[pre + "feed_forward.w2"].float(),
+                                         P[pre + "feed_forward.w3"].float())
+    return plain_llama.rms_norm(x, P["final_norm.weight"].float(), 1e-5) @ P["head.weight"].float().T
+
+
+def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(backend):
+    device, dtype = backend
+    if "running_mean" not in parts.MIXERS:
+        parts.register_mixer("running_mean", RunningMeanMixer)
+    spec = toy_spec()
+    model = Transformer(spec, dtype, device)
+    P = {}
+    for i, (name, ps) in enumerate(sorted(model.param_specs().items())):
+        t = rnd(*ps.shape, scale=0.15, seed=100 + i)
+        P[name] = bf16_exact(1 + t if ps.role == "vector" else t)
+    model.load_params({k: v.to(dtype if model.param_specs()[k].role == "matrix" else torch.float32).to(device)
+                       for k, v in P.items()})
+    needs = model.cache_needs()
+    assert needs[0].state is not None and needs[0].kv is None and needs[1].kv is not None and needs[2].state is not None
+    cache = model.new_cache(max_tokens=512)
+    assert len(cache.state_groups) == 1 and cache.state_groups[0].entries == [0, 2]
+    st = gf.Stepper(model, cache)
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(0, 61, (n,), generator=g).tolist() for n in (9, 1, 30)]
+    want = [toy_plain(s, P, spec) for s in seqs]
+    # whole, as one batch of unequal lengths
+    slots = cache.begin(3)
+    whole = st.step(slots, seqs, "all").cpu()
+    cache.end(slots)
+    # a head in one step, then one token at a time; the shorter sequences end earlier; slots are used again
+    slots = cache.begin(3)
+    assert float(cache.view(0).state[slots].abs().sum()) == 0.0                   # state starts at zero again
+    rows = {i: [] for i in range(3)}
+    heads = [max(1, len(s) - 5) for s in seqs]
+    out = st.step(slots, [s[:h] for s, h in zip(seqs, heads)], "all").cpu()
+    o = 0
+    for i, h in enumerate(heads):
+        rows[i] += list(out[o:o + h]); o += h
+    at = list(heads)
+    live = [i for i in range(3) if at[i] < len(seqs[i])]
+    while live:
+        out = st.step([slots[i] for i in live], [[seqs[i][at[i]]] for i in live], "last").cpu()
+        for k, i in enumerate(live):
+            rows[i].append(out[k]); at[i] += 1
+        live = [i for i in live if at[i] < len(seqs[i])]
+    st.check()
+    cache.end(slots)
+    o = 0
+    for i, s in enumerate(seqs):
+        torch.testing.assert_close(whole[o:o + len(s)], want[i], **tol(dtype))
+        torch.testing.assert_close(torch.stack(rows[i]), want[i], **tol(dtype))
+        o += len(s)
