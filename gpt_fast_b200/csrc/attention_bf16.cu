@@ -43,6 +43,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     __shared__ float red[MAX_REP][2];      // per head: (rescale of what was summed so far, sum of this tile)
     __shared__ float mrun[MAX_REP];        // per head: running maximum
 
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     const int t = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
     const int s = b.tok_seq[t];
     const int slot = b.slots[s];
@@ -202,6 +204,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
 
 __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
                                     __nv_bfloat16* __restrict__ out, int H, int d, int splits) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     const int t = blockIdx.x, head = blockIdx.y;
     const float* ml = scratch_ml + ((size_t)t * H + head) * splits * 2;
     float m = -INFINITY;
@@ -249,13 +253,14 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     float* so = scratch;
     float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
     dim3 grid(n_tokens, G, splits);
-    attn_decode_kernel<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b, H, G, d,
-                                                        scale * 1.4426950408889634f, window, splits, status);
-    if (gfb_check_launch("gfb_attn_decode")) return 1;
+    cudaError_t e = gfb_launch(attn_decode_kernel, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
+                               (__nv_bfloat16*)out, so, sml, kv, b, H, G, d, scale * 1.4426950408889634f, window, splits, status);
+    if (gfb_check(e, "gfb_attn_decode")) return 1;
     if (splits > 1) {
         dim3 cgrid(n_tokens, H);
-        attn_combine_kernel<<<cgrid, 128, 0, stream>>>(so, sml, (__nv_bfloat16*)out, H, d, splits);
-        return gfb_check_launch("gfb_attn_decode (combine)");
+        e = gfb_launch(attn_combine_kernel, cgrid, dim3(128), 0, stream, (const float*)so, (const float*)sml,
+                       (__nv_bfloat16*)out, H, d, splits);
+        return gfb_check(e, "gfb_attn_decode (combine)");
     }
     return 0;
 }

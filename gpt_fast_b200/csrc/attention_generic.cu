@@ -29,6 +29,8 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
     float* ps = smem + d;          // [CHUNK]
     __shared__ float scratch[32];
     __shared__ int page_of[CHUNK]; // page ids of the current chunk (2 pages of 64, or fewer larger ones)
+    gfb_pdl_launch();
+    gfb_pdl_wait();
 
     int t = blockIdx.x, h = blockIdx.y;
     int g = h / (H / G);
@@ -119,13 +121,14 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     dim3 grid(n_tokens, H);
     size_t smem = (size_t)(d + CHUNK) * sizeof(float);
+    cudaError_t e;
     if (dt == GFB_BF16)
-        attention_generic_kernel<__nv_bfloat16><<<grid, CHUNK, smem, stream>>>(
-            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, scale, window, status);
+        e = gfb_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream,
+                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, scale, window, status);
     else if (dt == GFB_F32)
-        attention_generic_kernel<float><<<grid, CHUNK, smem, stream>>>(
-            (const float*)q, (float*)out, kv, b, H, G, d, scale, window, status);
+        e = gfb_launch(attention_generic_kernel<float>, grid, dim3(CHUNK), smem, stream,
+                       (const float*)q, (float*)out, kv, b, H, G, d, scale, window, status);
     else
         return gfb_fail("gfb_attention_generic: unknown type %d", dt);
-    return gfb_check_launch("gfb_attention_generic");
+    return gfb_check(e, "gfb_attention_generic");
 }

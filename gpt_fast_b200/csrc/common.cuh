@@ -12,6 +12,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define GFB_API extern "C" __attribute__((visibility("default")))
 
@@ -53,6 +54,50 @@ static inline int gfb_check_launch(const char* what) {
 
 #define GFB_DEFINE_LAST_ERROR() \
     GFB_API const char* gfb_last_error() { return gfb_error_text; }
+
+// ---- launches with programmatic dependent launch -----------------------------------
+// Every kernel of the library is launched with the attribute that lets it start
+// while its predecessor in the stream is still draining: its blocks become
+// resident, set up (barriers, tensor memory, prefetch of weights, which no
+// earlier kernel writes) and then wait in `gfb_pdl_wait()` until the
+// predecessor has completed and its writes are visible.  A kernel calls
+// `gfb_pdl_launch()` once it holds the resources it needs, which allows its own
+// successor to become resident.  Because every block of every kernel executes
+// the wait before it touches anything an earlier kernel wrote, completion stays
+// ordered along the whole chain.  GFB_NO_PDL=1 in the environment turns the
+// attribute off (the two instructions are then no-ops).
+__device__ __forceinline__ void gfb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gfb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool gfb_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("GFB_NO_PDL");
+        on = (e != nullptr && e[0] == '1') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t gfb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gfb_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+static inline int gfb_check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) return gfb_fail("%s: %s", what, cudaGetErrorString(e));
+    return gfb_check_launch(what);
+}
 
 // ---- conversions ---------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float gfb_to_f32(T v);

@@ -11,6 +11,8 @@ GFB_DEFINE_LAST_ERROR()
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int D, int V, int* status) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     int t = blockIdx.x;
     int id = tokens[t];
     float* o = out + (size_t)t * D;
@@ -27,50 +29,90 @@ GFB_API int gfb_embed(const int* tokens, const void* table, int table_dt, float*
                       int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     int threads = D >= 1024 ? 256 : 128;
+    cudaError_t e;
     if (table_dt == GFB_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, D, V, status);
+        e = gfb_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, D, V, status);
     else if (table_dt == GFB_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, out, D, V, status);
+        e = gfb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, D, V, status);
     else
         return gfb_fail("gfb_embed: unknown table type %d", table_dt);
-    return gfb_check_launch("gfb_embed");
+    return gfb_check(e, "gfb_embed");
 }
 
 // ------------------------------------------------------------------ RMSNorm --
 // out[r] = x[row(r)] * rsqrt(mean(x^2) + eps) * w, statistics and product in
 // 32-bit, one rounding at the store.  `rows` (optional) gathers input rows.
+// With `pending` ([S][T][D] partial sums of a product split over K that still
+// have to be added to the residual x) the kernel first completes the residual
+// sum, x[row] += sum_s pending[s][row] in ascending s, writes x back and norms
+// the result: the reduction of the split, the residual add and the norm are
+// one pass over the row.
 template <typename TW, typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                               const int* __restrict__ rows, int D, float eps) {
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int S, size_t slice,
+                               const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows,
+                               int D, float eps) {
     __shared__ float scratch[32];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    size_t row = (size_t)(rows ? rows[r] : r) * D;
+    float* xr = x + row;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+    if (pending != nullptr) {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            float v = xr[i];
+            for (int k = 0; k < S; k++) v += pending[(size_t)k * slice + row + i];
+            xr[i] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+    }
     ss = gfb_block_sum(ss, scratch);
     float rstd = rsqrtf(ss / (float)D + eps);
     TO* o = out + (size_t)r * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_from_f32<TO>(xr[i] * rstd * gfb_to_f32(w[i]));
 }
 
-GFB_API int gfb_rmsnorm(const float* x, const void* w, int w_dt, void* out, int out_dt, const int* rows,
-                        int R, int D, float eps, cudaStream_t stream) {
+GFB_API int gfb_rmsnorm(float* x, const float* pending, int S, long slice, const void* w, int w_dt, void* out, int out_dt,
+                        const int* rows, int R, int D, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
+    if (pending != nullptr && rows != nullptr) return gfb_fail("gfb_rmsnorm: pending partial sums cannot be combined with a row gather");
     int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
-#define LAUNCH(TW, TO) rmsnorm_kernel<TW, TO><<<R, threads, 0, stream>>>(x, (const TW*)w, (TO*)out, rows, D, eps)
+    cudaError_t e;
+#define LAUNCH(TW, TO) e = gfb_launch(rmsnorm_kernel<TW, TO>, dim3(R), dim3(threads), 0, stream, x, pending, S, (size_t)slice, (const TW*)w, (TO*)out, rows, D, eps)
     if (w_dt == GFB_BF16 && out_dt == GFB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (w_dt == GFB_F32 && out_dt == GFB_BF16) LAUNCH(float, __nv_bfloat16);
     else if (w_dt == GFB_BF16 && out_dt == GFB_F32) LAUNCH(__nv_bfloat16, float);
     else if (w_dt == GFB_F32 && out_dt == GFB_F32) LAUNCH(float, float);
     else return gfb_fail("gfb_rmsnorm: unknown types %d %d", w_dt, out_dt);
 #undef LAUNCH
-    return gfb_check_launch("gfb_rmsnorm");
+    return gfb_check(e, "gfb_rmsnorm");
+}
+
+// x += sum_s pending[s] (ascending s): completes a residual sum whose product was split over K.
+__global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ pending, int S, size_t n) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    for (int k = 0; k < S; k++) v += pending[(size_t)k * n + i];
+    x[i] = v;
+}
+
+GFB_API int gfb_add_partials(float* x, const float* pending, int S, long n, cudaStream_t stream) {
+    if (n <= 0 || S <= 0) return 0;
+    cudaError_t e = gfb_launch(add_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, pending, S, (size_t)n);
+    return gfb_check(e, "gfb_add_partials");
 }
 
 // ------------------------------------------------------------- rotary table --
 // table[p][i] = (cos, sin)(p * inv_freq[i]); the angle is the 32-bit product,
 // cosf/sinf are the accurate versions (this file is built without fast-math).
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ table, int P, int half) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= P * half) return;
     int p = idx / half, i = idx - p * half;
@@ -82,8 +124,8 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __r
 GFB_API int gfb_rope_table(const float* inv_freq, float* table, int P, int half, cudaStream_t stream) {
     long total = (long)P * half;
     if (total <= 0) return 0;
-    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, table, P, half);
-    return gfb_check_launch("gfb_rope_table");
+    cudaError_t e = gfb_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, inv_freq, table, P, half);
+    return gfb_check(e, "gfb_rope_table");
 }
 
 // ------------------------------------------------- rotary + cache append -----
@@ -91,62 +133,75 @@ GFB_API int gfb_rope_table(const float* inv_freq, float* table, int P, int half,
 // absolute position; q goes to q_out, k and v go to the token's place in the
 // paged cache.  pairing 0: pairs (2i, 2i+1); pairing 1: pairs (i, i + d/2).
 // append = 0: only q is produced (the layer reads a cache another layer wrote).
-template <typename T>
-__global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, GfbPagedKV kv, GfbBatch b,
-                                   const float* __restrict__ table, int table_len, int H, int G, int d,
-                                   int pairing, int append, int* status) {
-    int t = blockIdx.x;
-    int s = b.tok_seq[t];
-    int slot = b.slots[s];
-    int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
-    int half = d >> 1;
+// The input is either qkv in the model's type, or (PARTIAL) the 32-bit partial
+// sums [S][T][(H+2G)d] of a product split over K, which are summed here in
+// ascending s: the split's reduction costs no kernel of its own.
+// One thread per pair of elements: block y of token x handles 256 pairs.
+template <typename T, bool PARTIAL>
+__global__ void rope_append_kernel(const void* __restrict__ src_any, int S, size_t slice, T* __restrict__ q_out,
+                                   GfbPagedKV kv, GfbBatch b, const float* __restrict__ table, int table_len,
+                                   int H, int G, int d, int pairing, int append, int* status) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int t = blockIdx.x;
+    const int half = d >> 1;
+    const int n_rot = (H + (append ? G : 0)) * half;          // rotated pairs
+    const int n_items = n_rot + (append ? G * half : 0);      // + pairs of v that are copied
+    const int item = blockIdx.y * blockDim.x + threadIdx.x;
+    if (item >= n_items) return;
+    const int s = b.tok_seq[t];
+    const int slot = b.slots[s];
+    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
     bool ok = pos >= 0 && pos < table_len;
-    T* kdst = nullptr;
-    T* vdst = nullptr;
+    size_t cache_base = 0;
     if (append) {
         int pi = pos / kv.page_size, off = pos - pi * kv.page_size;
         int page = (ok && pi < kv.max_pages) ? kv.page_table[(size_t)slot * kv.max_pages + pi] : -1;
-        if (page < 0 || page >= kv.n_pages) {
-            ok = false;
-        } else {
-            size_t base = ((size_t)page * G * kv.page_size + off) * d;   // + g * page_size * d
-            kdst = (T*)kv.k_pool + base;
-            vdst = (T*)kv.v_pool + base;
-        }
+        if (page < 0 || page >= kv.n_pages) ok = false;
+        else cache_base = ((size_t)page * G * kv.page_size + off) * d;          // + g * page_size * d
     }
+    const bool rot = item < n_rot;
+    const int head = rot ? item / half : H + G + (item - n_rot) / half;
+    const int i = rot ? item - head * half : (item - n_rot) % half;
+    const int i0 = (rot && pairing == 1) ? i : 2 * i;
+    const int i1 = (rot && pairing == 1) ? i + half : 2 * i + 1;
     if (!ok) {
-        if (threadIdx.x == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
-        // q_out stays defined (zeros) so that later kernels read no garbage
-        for (int i = threadIdx.x; i < H * d; i += blockDim.x) q_out[(size_t)t * H * d + i] = gfb_from_f32<T>(0.f);
+        if (item == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+        if (head < H) {                                       // q stays defined so that later kernels read no garbage
+            T* dst = q_out + ((size_t)t * H + head) * d;
+            dst[i0] = gfb_from_f32<T>(0.f);
+            dst[i1] = gfb_from_f32<T>(0.f);
+        }
         return;
     }
-    const T* src = qkv + (size_t)t * (H + 2 * G) * d;
-    const float* cs = table + (size_t)pos * half * 2;
-    int rot_pairs = (H + (append ? G : 0)) * half;
-    for (int idx = threadIdx.x; idx < rot_pairs; idx += blockDim.x) {
-        int head = idx / half, i = idx - head * half;
-        int i0 = pairing == 0 ? 2 * i : i;
-        int i1 = pairing == 0 ? 2 * i + 1 : i + half;
-        const T* hsrc = src + (size_t)head * d;
-        float x0 = gfb_to_f32(hsrc[i0]), x1 = gfb_to_f32(hsrc[i1]);
-        float c = cs[2 * i], sn = cs[2 * i + 1];
-        float o0 = x0 * c - x1 * sn;
-        float o1 = x1 * c + x0 * sn;
-        T* dst = head < H ? q_out + ((size_t)t * H + head) * d
-                          : kdst + (size_t)(head - H) * kv.page_size * d;
-        dst[i0] = gfb_from_f32<T>(o0);
-        dst[i1] = gfb_from_f32<T>(o1);
+    const size_t W = (size_t)(H + 2 * G) * d;
+    const size_t e0 = (size_t)t * W + (size_t)head * d + i0, e1 = (size_t)t * W + (size_t)head * d + i1;
+    float x0, x1;
+    if (PARTIAL) {
+        const float* p = (const float*)src_any;
+        x0 = 0.f; x1 = 0.f;
+        for (int k = 0; k < S; k++) { x0 += p[(size_t)k * slice + e0]; x1 += p[(size_t)k * slice + e1]; }
+    } else {
+        const T* p = (const T*)src_any;
+        x0 = gfb_to_f32(p[e0]); x1 = gfb_to_f32(p[e1]);
     }
-    if (append) {
-        const T* vsrc = src + (size_t)(H + G) * d;
-        for (int idx = threadIdx.x; idx < G * d; idx += blockDim.x) {
-            int g = idx / d, i = idx - g * d;
-            vdst[(size_t)g * kv.page_size * d + i] = vsrc[idx];
-        }
+    T* dst;
+    if (head < H) dst = q_out + ((size_t)t * H + head) * d;
+    else if (head < H + G) dst = (T*)kv.k_pool + cache_base + (size_t)(head - H) * kv.page_size * d;
+    else dst = (T*)kv.v_pool + cache_base + (size_t)(head - H - G) * kv.page_size * d;
+    if (rot) {
+        const float* cs = table + ((size_t)pos * half + i) * 2;
+        float c = cs[0], sn = cs[1];
+        dst[i0] = gfb_from_f32<T>(x0 * c - x1 * sn);
+        dst[i1] = gfb_from_f32<T>(x1 * c + x0 * sn);
+    } else {
+        dst[i0] = gfb_from_f32<T>(x0);
+        dst[i1] = gfb_from_f32<T>(x1);
     }
 }
 
-GFB_API int gfb_rope_append(const void* qkv, void* q_out, int dt,
+// src: qkv [T, (H+2G)d] of type dt, or, with n_partials > 0, float partial sums [n_partials][T][(H+2G)d].
+GFB_API int gfb_rope_append(const void* src, int n_partials, void* q_out, int dt,
                             void* k_pool, void* v_pool, const int* page_table, int max_pages, int page_size, int n_pages,
                             const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
                             int n_seqs, int n_tokens,
@@ -156,34 +211,40 @@ GFB_API int gfb_rope_append(const void* qkv, void* q_out, int dt,
     if (d % 2) return gfb_fail("gfb_rope_append: head_dim %d is odd", d);
     GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
-    int work = (H + G) * d / 2;
-    int threads = work >= 1024 ? 256 : 128;
-    if (dt == GFB_BF16)
-        rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, kv, b, table, table_len, H, G, d, pairing, append, status);
-    else if (dt == GFB_F32)
-        rope_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            (const float*)qkv, (float*)q_out, kv, b, table, table_len, H, G, d, pairing, append, status);
-    else
-        return gfb_fail("gfb_rope_append: unknown type %d", dt);
-    return gfb_check_launch("gfb_rope_append");
+    int items = (H + (append ? 2 * G : 0)) * (d / 2);
+    dim3 grid(n_tokens, (items + 255) / 256);
+    if (grid.y > 65535) return gfb_fail("gfb_rope_append: %d heads of %d exceed the grid", H + 2 * G, d);
+    size_t slice = (size_t)n_tokens * (H + 2 * G) * d;
+    cudaError_t e;
+#define GO(T, P) e = gfb_launch(rope_append_kernel<T, P>, grid, dim3(256), 0, stream, src, n_partials, slice, (T*)q_out, kv, b, table, table_len, H, G, d, pairing, append, status)
+    if (dt == GFB_BF16 && n_partials > 0) GO(__nv_bfloat16, true);
+    else if (dt == GFB_BF16) GO(__nv_bfloat16, false);
+    else if (dt == GFB_F32 && n_partials > 0) GO(float, true);
+    else if (dt == GFB_F32) GO(float, false);
+    else return gfb_fail("gfb_rope_append: unknown type %d", dt);
+#undef GO
+    return gfb_check(e, "gfb_rope_append");
 }
 
 // --------------------------------------------------------------- bookkeeping --
 __global__ void advance_lengths_kernel(int* lengths, const int* slots, const int* cu_seqlens, int n) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) lengths[slots[i]] += cu_seqlens[i + 1] - cu_seqlens[i];
 }
 
 GFB_API int gfb_advance_lengths(int* lengths, const int* slots, const int* cu_seqlens, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    advance_lengths_kernel<<<(n + 127) / 128, 128, 0, stream>>>(lengths, slots, cu_seqlens, n);
-    return gfb_check_launch("gfb_advance_lengths");
+    cudaError_t e = gfb_launch(advance_lengths_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, lengths, slots, cu_seqlens, n);
+    return gfb_check(e, "gfb_advance_lengths");
 }
 
 // out (32-bit) += y: for parts that do not fuse the residual sum into a product.
 template <typename T>
 __global__ void add_into_kernel(float* __restrict__ out, const T* __restrict__ y, size_t n) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] += gfb_to_f32(y[i]);
 }
@@ -191,8 +252,9 @@ __global__ void add_into_kernel(float* __restrict__ out, const T* __restrict__ y
 GFB_API int gfb_add_into(float* out, const void* y, int dt, long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dt == GFB_BF16) add_into_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(out, (const __nv_bfloat16*)y, (size_t)n);
-    else if (dt == GFB_F32) add_into_kernel<float><<<blocks, 256, 0, stream>>>(out, (const float*)y, (size_t)n);
+    cudaError_t e;
+    if (dt == GFB_BF16) e = gfb_launch(add_into_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, out, (const __nv_bfloat16*)y, (size_t)n);
+    else if (dt == GFB_F32) e = gfb_launch(add_into_kernel<float>, dim3(blocks), dim3(256), 0, stream, out, (const float*)y, (size_t)n);
     else return gfb_fail("gfb_add_into: unknown type %d", dt);
-    return gfb_check_launch("gfb_add_into");
+    return gfb_check(e, "gfb_add_into");
 }

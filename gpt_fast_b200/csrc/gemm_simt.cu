@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M, int N, int K) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     float acc[4][4];
@@ -89,13 +91,14 @@ template <typename TA, typename TW, typename TC>
 static int launch(const void* A, const void* W, void* C, int M, int N, int K, int epi, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return gfb_fail("gfb_gemm_simt: M = %d is too large", M);
-#define GO(E) gemm_simt_kernel<TA, TW, TC, E><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K)
+    cudaError_t e;
+#define GO(E) e = gfb_launch(gemm_simt_kernel<TA, TW, TC, E>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K)
     if (epi == EPI_STORE) GO(EPI_STORE);
     else if (epi == EPI_ADD) GO(EPI_ADD);
     else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU);
     else return gfb_fail("gfb_gemm_simt: unknown epilogue %d", epi);
 #undef GO
-    return gfb_check_launch("gfb_gemm_simt");
+    return gfb_check(e, "gfb_gemm_simt");
 }
 
 // in_dt: type of A and W; out_dt: type of C (ADD needs 32-bit C).

@@ -234,10 +234,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    // This block now holds everything it needs (shared memory, tensor memory): the next kernel
+    // in the stream may become resident.  Weights are written by no kernel, so the producer
+    // fills the ring with weight tiles before it waits for the previous kernel; everything
+    // else (activations, the residual, the partials) is touched only after the wait.
+    gfb_pdl_launch();
+    if (!(warp == 0 && lane == 0)) gfb_pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; i++) {
+            const int n_pre = min(stages, nkb);
+            for (int i = 0; i < n_pre; i++) {               // fresh barriers: every stage is free
+                uint32_t full = smem_u32(&bars->full[i]);
+                mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                if (SWAP) tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
+                else tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
+            }
+            gfb_pdl_wait();
+            for (int i = 0; i < n_pre; i++) {
+                uint32_t full = smem_u32(&bars->full[i]);
+                if (SWAP) tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
+                else tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
+            }
+            for (int i = n_pre; i < nkb; i++) {
                 int s = i % stages;
                 uint32_t ph = (uint32_t)(i / stages) & 1u;
                 if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
@@ -318,6 +337,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // partial: [S][M][N] f32.
 template <int EPI, typename TO>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TO* __restrict__ out, int S, int M, int N, int ldo) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     int n = blockIdx.x * blockDim.x + threadIdx.x;
     int m = blockIdx.y;
     if (EPI == EPI_SWIGLU) {
@@ -389,8 +410,8 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* parti
         configured = smem;
     }
     dim3 grid((R + BM - 1) / BM, (Cc + BN - 1) / BN, splits);
-    kern<<<grid, 192, smem, stream>>>(mx, my, (TO*)out, partial, R, Cc, K, ldo, kb_per_split, stages, status);
-    return gfb_check_launch("gfb_gemm_tc");
+    cudaError_t e = gfb_launch(kern, grid, dim3(192), smem, stream, mx, my, (TO*)out, partial, R, Cc, K, ldo, kb_per_split, stages, status);
+    return gfb_check(e, "gfb_gemm_tc");
 }
 
 template <int BN, bool SWAP>
@@ -411,9 +432,13 @@ int dispatch_epi(int epi, int out_dt, const CUtensorMap& mx, const CUtensorMap& 
 
 // out = A[M,K] * W[N,K]^T with the epilogue `epi`.  swap = 0: 128 tokens x bn weight rows per tile
 // (bn 128 or 256); swap = 1: 128 weight rows x bn tokens (bn 16, 32, 64 or 128, M <= bn * tiles).
-// splits > 1 (swap only) writes partials to `workspace` ([splits, M, N] f32) and reduces them.
+// splits > 1 (swap only) writes partials to `workspace` ([splits, M, N] f32); with reduce != 0 they are
+// summed and the epilogue applied by a second kernel, with reduce == 0 the caller's next kernel consumes
+// them.  *splits_used receives the number of slices that were written.
 GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int M, int N, int K, int epi, int swap,
-                        int bn, int splits, int stages, float* workspace, int* status, cudaStream_t stream) {
+                        int bn, int splits, int stages, float* workspace, int reduce, int* splits_used, int* status,
+                        cudaStream_t stream) {
+    if (splits_used) *splits_used = 1;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8) return gfb_fail("gfb_gemm_tc: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (N % 8) return gfb_fail("gfb_gemm_tc: N = %d must be a multiple of 8", N);
@@ -426,6 +451,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     if (splits > total_kb) splits = total_kb;
     int kbps = (total_kb + splits - 1) / splits;
     splits = (total_kb + kbps - 1) / kbps;                 // no empty split
+    if (splits_used) *splits_used = splits;
     if (splits > 1 && !swap) return gfb_fail("gfb_gemm_tc: a split over K needs the swapped orientation");
     if (splits > 1 && workspace == nullptr) return gfb_fail("gfb_gemm_tc: a split over K needs a workspace");
 
@@ -446,17 +472,18 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     else return gfb_fail("gfb_gemm_tc: no kernel for swap = %d, bn = %d", swap, bn);
 #undef BNCASE
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && reduce) {
         typedef __nv_bfloat16 bf16;
         int cols = epi == EPI_SWIGLU ? N / 2 : N;
         dim3 grid((cols + 255) / 256, M);
-#define RED(E, T) splitk_reduce_kernel<E, T><<<grid, 256, 0, stream>>>(workspace, (T*)out, splits, M, N, ldo)
+        cudaError_t e;
+#define RED(E, T) e = gfb_launch(splitk_reduce_kernel<E, T>, grid, dim3(256), 0, stream, (const float*)workspace, (T*)out, splits, M, N, ldo)
         if (epi == EPI_ADD) RED(EPI_ADD, float);
         else if (epi == EPI_SWIGLU) RED(EPI_SWIGLU, bf16);
         else if (out_dt == GFB_F32) RED(EPI_STORE, float);
         else RED(EPI_STORE, bf16);
 #undef RED
-        return gfb_check_launch("gfb_gemm_tc (split reduce)");
+        return gfb_check(e, "gfb_gemm_tc (split reduce)");
     }
     return 0;
 }

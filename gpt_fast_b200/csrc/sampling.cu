@@ -84,6 +84,8 @@ __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
     float v = -INFINITY;
     int idx = 0x7fffffff;
@@ -107,6 +109,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
     __shared__ int si[32];
     __shared__ uint32_t sh_prefix;
     __shared__ int sh_remaining;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
 
     // pivot = k-th largest scaled logit (everything when top_k <= 0 or >= V)
@@ -166,8 +170,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
 GFB_API int gfb_argmax(const float* logits, int* out, int B, int V, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return gfb_fail("gfb_argmax: V = %d", V);
-    argmax_kernel<<<B, THREADS, 0, stream>>>(logits, out, V);
-    return gfb_check_launch("gfb_argmax");
+    cudaError_t e = gfb_launch(argmax_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V);
+    return gfb_check(e, "gfb_argmax");
 }
 
 GFB_API int gfb_sample(const float* logits, int* out, int B, int V, float temperature, int top_k,
@@ -176,7 +180,7 @@ GFB_API int gfb_sample(const float* logits, int* out, int B, int V, float temper
     if (B <= 0) return 0;
     if (V <= 0) return gfb_fail("gfb_sample: V = %d", V);
     float t = temperature > 1e-5f ? temperature : 1e-5f;
-    sample_kernel<<<B, THREADS, 0, stream>>>(logits, out, V, t, top_k, (uint64_t)seed,
-                                             (const int64_t*)request_ids, token_index, index_map, noise_out);
-    return gfb_check_launch("gfb_sample");
+    cudaError_t e = gfb_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V, t, top_k, (uint64_t)seed,
+                               (const int64_t*)request_ids, token_index, index_map, noise_out);
+    return gfb_check(e, "gfb_sample");
 }

@@ -15,6 +15,7 @@ from .. import ops
 from ..cache import Cache, CacheNeeds
 from ..config.spec import ModelSpec, PartSpec
 from ..ops.types import BatchMeta
+from ..parts.residual import Residual
 from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, build_part
 from ..weights.loader import ParamSpec
 
@@ -153,6 +154,7 @@ class Transformer:
         T = batch.n_tokens
         x = torch.empty(T, self.dim, dtype=torch.float32, device=self.device)
         ops.embed(tokens, self.embed_weight, x, batch.status)
+        x = Residual(x)
         for e in self.spec.schedule:
             self.blocks[e.layer].forward(x, batch, cache.view(e.cache), append=e.owns_cache)
         W = T if want_rows is None else (n_want if n_want is not None else want_rows.shape[0])

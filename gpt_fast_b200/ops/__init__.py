@@ -71,17 +71,30 @@ def embed(tokens, table, out, status):
     return kernels().embed(tokens, table, out, status)
 
 
-def rmsnorm(x, weight, eps: float, out, rows=None):
+def rmsnorm(x, weight, eps: float, out, rows=None, pending=None):
     """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight.  x float32
-    [T, D]; weight [D] (bfloat16 or float32); out [R, D]; rows int32 [R] or None."""
-    return kernels().rmsnorm(x, weight, eps, out, rows)
+    [T, D]; weight [D] (bfloat16 or float32); out [R, D]; rows int32 [R] or None.
+    pending (float32 [S, T, D], only without rows): partial sums still owed to x;
+    the kernel first completes x += sum_s pending[s] (written back), then norms."""
+    return kernels().rmsnorm(x, weight, eps, out, rows, pending)
 
 
-def linear(a, w, out, mode: str = "store"):
+def linear(a, w, out, mode: str = "store", defer: bool = False):
     """a [M, K] times w [N, K] transposed.  mode 'store': out [M, N] = product;
     'add': out float32 [M, N] += product (the residual sum, in 32-bit);
-    'swiglu': w's rows alternate gate, up and out [M, N/2] = silu(gate) * up."""
-    return kernels().linear(a, w, out, mode)
+    'swiglu': w's rows alternate gate, up and out [M, N/2] = silu(gate) * up.
+
+    defer=True (modes 'store' and 'add'): if the kernel splits the sum over K it
+    may return the partial sums (float32 [S, M, N]) INSTEAD of finishing `out`;
+    the caller hands them to the kernel that consumes the result (`rmsnorm`'s
+    `pending`, `rope_append`'s `partials`, or `add_partials`).  Returns None when
+    `out` is complete."""
+    return kernels().linear(a, w, out, mode, defer)
+
+
+def add_partials(x, pending):
+    """x (float32 [T, D]) += sum_s pending[s] in ascending s."""
+    return kernels().add_partials(x, pending)
 
 
 def rope_table(inv_freq, table):
@@ -90,11 +103,12 @@ def rope_table(inv_freq, table):
 
 
 def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n_kv: int, head_dim: int,
-                pairing: str = "interleaved", append: bool = True):
+                pairing: str = "interleaved", append: bool = True, partials=None):
     """Rotate the q and k heads of qkv [T, (H+2G)d] by each token's position;
     q goes to q_out [T, H, d]; k and v go to the token's place in the cache
-    (unless append is False)."""
-    return kernels().rope_append(qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing, append)
+    (unless append is False).  With partials (float32 [S, T, (H+2G)d], the
+    deferred result of `linear`) qkv is their sum and the `qkv` argument is not read."""
+    return kernels().rope_append(qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing, append, partials)
 
 
 def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, head_dim: int, scale: float,

@@ -81,7 +81,7 @@ class CudaKernels:
         self._call("core", "gfb_embed", _ptr(tokens), _ptr(table), c_int(_dt(table)), _ptr(out),
                    c_int(T), c_int(D), c_int(V), _ptr(status), _stream())
 
-    def rmsnorm(self, x, weight, eps, out, rows=None):
+    def rmsnorm(self, x, weight, eps, out, rows=None, pending=None):
         D = x.shape[-1]
         R = out.shape[0]
         _need(x, torch.float32, name="norm input")
@@ -89,10 +89,22 @@ class CudaKernels:
         _need(out, shape=(R, D), name="norm output")
         if rows is not None:
             _need(rows, torch.int32, (R,), "rows")
+            if pending is not None:
+                self.add_partials(x, pending)
+                pending = None
         elif x.shape[0] != R:
             _fail(f"norm output has {R} rows, input {x.shape[0]}")
-        self._call("core", "gfb_rmsnorm", _ptr(x), _ptr(weight), c_int(_dt(weight)), _ptr(out), c_int(_dt(out)),
-                   _ptr(rows), c_int(R), c_int(D), c_float(eps), _stream())
+        S = 0
+        if pending is not None:
+            S = pending.shape[0]
+            _need(pending, torch.float32, (S,) + tuple(x.shape), "pending partial sums")
+        self._call("core", "gfb_rmsnorm", _ptr(x), _ptr(pending), c_int(S), c_long(x.numel()), _ptr(weight),
+                   c_int(_dt(weight)), _ptr(out), c_int(_dt(out)), _ptr(rows), c_int(R), c_int(D), c_float(eps), _stream())
+
+    def add_partials(self, x, pending):
+        _need(x, torch.float32, name="sum")
+        _need(pending, torch.float32, (pending.shape[0],) + tuple(x.shape), "pending partial sums")
+        self._call("core", "gfb_add_partials", _ptr(x), _ptr(pending), c_int(pending.shape[0]), c_long(x.numel()), _stream())
 
     def rope_table(self, inv_freq, table):
         P, half, two = table.shape
@@ -107,16 +119,23 @@ class CudaKernels:
         return (_ptr(kv.k_pool), _ptr(kv.v_pool), _ptr(kv.page_table), c_int(kv.page_table.shape[1]),
                 c_int(kv.page_size), c_int(kv.k_pool.shape[0]))
 
-    def rope_append(self, qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing, append):
+    def rope_append(self, qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing, append, partials=None):
         T = batch.n_tokens
-        _need(qkv, shape=(T, (n_head + 2 * n_kv) * head_dim), name="qkv")
-        _need(q_out, qkv.dtype, (T, n_head, head_dim), "q_out")
+        W = (n_head + 2 * n_kv) * head_dim
+        if partials is not None:
+            _need(partials, torch.float32, (partials.shape[0], T, W), "partial sums of qkv")
+            src, n_part = partials, partials.shape[0]
+        else:
+            _need(qkv, shape=(T, W), name="qkv")
+            src, n_part = qkv, 0
+        _need(q_out, shape=(T, n_head, head_dim), name="q_out")
+        qkv = q_out                                     # the element type of the outputs
         _need(table, torch.float32, name="rotary table")
         if append:
             _need(kv.k_pool, qkv.dtype, name="key pool")
             if tuple(kv.k_pool.shape[1:]) != (n_kv, kv.page_size, head_dim):
                 _fail(f"key pool pages are {tuple(kv.k_pool.shape[1:])}, the layer needs {(n_kv, kv.page_size, head_dim)}")
-        self._call("core", "gfb_rope_append", _ptr(qkv), _ptr(q_out), c_int(_dt(qkv)), *self._kv_args(kv),
+        self._call("core", "gfb_rope_append", _ptr(src), c_int(n_part), _ptr(q_out), c_int(_dt(q_out)), *self._kv_args(kv),
                    *self._batch_args(batch), _ptr(table), c_int(table.shape[0]), c_int(n_head), c_int(n_kv),
                    c_int(head_dim), c_int(_PAIRING[pairing]), c_int(1 if append else 0), _ptr(batch.status), _stream())
 
@@ -130,7 +149,7 @@ class CudaKernels:
         self._call("core", "gfb_add_into", _ptr(out), _ptr(y), c_int(_dt(y)), c_long(out.numel()), _stream())
 
     # -- matrix products -----------------------------------------------------------
-    def linear(self, a, w, out, mode="store"):
+    def linear(self, a, w, out, mode="store", defer=False):
         M, K = a.shape
         N = w.shape[0]
         _need(a, name="activation")
@@ -142,7 +161,7 @@ class CudaKernels:
         if mode != "add" and out.dtype not in (a.dtype, torch.float32):
             _fail(f"product of {a.dtype} cannot be stored as {out.dtype}")
         if a.dtype == torch.bfloat16 and self._tc_fits(M, N, K, mode):
-            return self._linear_tc(a, w, out, mode)
+            return self._linear_tc(a, w, out, mode, defer=defer and mode in ("store", "add"))
         if a.dtype == torch.float32 and out.dtype != torch.float32:
             _fail("a float32 product is stored as float32")
         self._call("gemm_simt", "gfb_gemm_simt", _ptr(a), _ptr(w), _ptr(out), c_int(_dt(a)), c_int(_dt(out)),
@@ -180,14 +199,18 @@ class CudaKernels:
             self._status = torch.zeros(4, dtype=torch.int32, device="cuda")
         return self._status
 
-    def _linear_tc(self, a, w, out, mode, plan=None):
+    def _linear_tc(self, a, w, out, mode, plan=None, defer=False):
         M, K = a.shape
         N = w.shape[0]
         swap, bn, splits, stages = plan or self.tc_plan(M, N, K)
         ws = torch.empty(splits, M, N, dtype=torch.float32, device=a.device) if splits > 1 else None
+        used = c_int(1)
         self._call("gemm_tc", "gfb_gemm_tc", _ptr(a), _ptr(w), _ptr(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
                    c_int(_EPI[mode]), c_int(swap), c_int(bn), c_int(splits), c_int(stages), _ptr(ws),
-                   _ptr(self.status), _stream())
+                   c_int(0 if defer else 1), ctypes.byref(used), _ptr(self.status), _stream())
+        if defer and used.value > 1:
+            return ws[:used.value]
+        return None
 
     # -- attention ---------------------------------------------------------------------
     def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None):

@@ -11,9 +11,10 @@ sees the model's configuration.  Five kinds, one registry each:
     BLOCKS         forward(x32, batch, view, append): the arrangement of the above
 
 Every part also has `param_specs()` (name -> weights.loader.ParamSpec) and
-`load(tensors)`.  Mixers and feed-forwards ADD their result into `residual`
-(float32, in place): the residual sum is part of the producing kernel where
-that is possible, `ops.add_into` otherwise.
+`load(tensors)`.  Mixers and feed-forwards ADD their result into `residual`, the
+step's residual stream (`parts.residual.Residual`, float32):
+`residual.add_linear(a, w)` folds the sum into the product's kernel (or defers
+it to the next norm), `residual.add(y)` is for parts that cannot fuse.
 
 `register_*` adds a class under a name; a `config.spec.PartSpec` names it.
 """

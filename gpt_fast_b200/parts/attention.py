@@ -14,6 +14,7 @@ from .. import ops
 from ..cache.needs import CacheNeeds, KVNeed
 from ..weights.loader import ParamSpec
 from . import register_mixer
+from .residual import as_residual
 
 
 @register_mixer("attention")
@@ -46,9 +47,9 @@ class Attention:
         T = batch.n_tokens
         H, G, d = self.n_head, self.n_kv, self.head_dim
         qkv = torch.empty(T, (H + 2 * G) * d, dtype=self.dtype, device=h.device)
-        ops.linear(h, self.wqkv, qkv)
+        partials = ops.linear(h, self.wqkv, qkv, defer=True)      # a split sum is finished by the rotary kernel
         q = torch.empty(T, H, d, dtype=self.dtype, device=h.device)
-        ops.rope_append(qkv, q, view.kv, batch, self.position.table, H, G, d, self.position.pairing, append)
+        ops.rope_append(qkv, q, view.kv, batch, self.position.table, H, G, d, self.position.pairing, append, partials)
         y = torch.empty(T, H * d, dtype=self.dtype, device=h.device)
         ops.attention(q, view.kv, batch, y, H, G, d, self.scale, self.window)
-        ops.linear(y, self.wo, residual, mode="add")
+        as_residual(residual).add_linear(y, self.wo)

@@ -4,6 +4,7 @@ residual stream x kept in 32-bit."""
 import torch
 
 from . import register_block
+from .residual import as_residual
 
 
 @register_block("prenorm")
@@ -18,7 +19,9 @@ class PreNormBlock:
                 "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
 
     def forward(self, x, batch, view, append: bool = True):
-        h = torch.empty(x.shape[0], self.dim, dtype=self.dtype, device=x.device)
+        """x: the residual stream (`parts.residual.Residual`), updated in place."""
+        x = as_residual(x)
+        h = torch.empty(x.x.shape[0], self.dim, dtype=self.dtype, device=x.x.device)
         self.mixer_norm.forward(x, h)
         self.mixer.forward(h, batch, view, residual=x, append=append)
         self.ffn_norm.forward(x, h)

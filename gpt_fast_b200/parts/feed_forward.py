@@ -8,6 +8,7 @@ import torch
 from .. import ops
 from ..weights.loader import ParamSpec
 from . import register_feed_forward
+from .residual import as_residual
 
 
 @register_feed_forward("swiglu")
@@ -27,4 +28,4 @@ class SwiGLU:
     def forward(self, h, residual):
         act = torch.empty(h.shape[0], self.hidden, dtype=self.dtype, device=h.device)
         ops.linear(h, self.w13, act, mode="swiglu")
-        ops.linear(act, self.w2, residual, mode="add")
+        as_residual(residual).add_linear(act, self.w2)

@@ -5,6 +5,7 @@ import torch
 from .. import ops
 from ..weights.loader import ParamSpec
 from . import register_norm
+from .residual import Residual
 
 
 @register_norm("rmsnorm")
@@ -20,7 +21,12 @@ class RMSNorm:
         self.weight = tensors["weight"]
 
     def forward(self, x, out, rows=None):
-        """x float32 [T, dim] -> out [R, dim] in the compute dtype; `rows`
-        (int32 [R]) picks input rows, else R = T."""
-        ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        """x: the residual stream (a `Residual`, or a complete float32 tensor
+        [T, dim]) -> out [R, dim] in the compute dtype; `rows` (int32 [R]) picks
+        input rows, else R = T.  Partial sums pending on the stream are added
+        by the same kernel."""
+        if isinstance(x, Residual):
+            ops.rmsnorm(x.x, self.weight, self.eps, out, rows, x.take_pending())
+        else:
+            ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out

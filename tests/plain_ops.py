@@ -66,7 +66,9 @@ class PlainOps:
         out.copy_(table[ids.clamp(0, table.shape[0] - 1)].float())
         out[bad] = 0
 
-    def rmsnorm(self, x, weight, eps, out, rows=None):
+    def rmsnorm(self, x, weight, eps, out, rows=None, pending=None):
+        if pending is not None:
+            self.add_partials(x, pending)
         xr = (x if rows is None else x[rows.long()]).double()
         n = xr * torch.rsqrt((xr * xr).mean(-1, keepdim=True) + eps)
         out.copy_((n * weight.double()).to(out.dtype))
@@ -76,9 +78,15 @@ class PlainOps:
         table[..., 0] = torch.cos(ang.double()).float()
         table[..., 1] = torch.sin(ang.double()).float()
 
-    def rope_append(self, qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing="interleaved", append=True):
+    def add_partials(self, x, pending):
+        x.copy_((x.double() + pending.double().sum(0)).float())
+
+    def rope_append(self, qkv, q_out, kv, batch, table, n_head, n_kv, head_dim, pairing="interleaved", append=True,
+                    partials=None):
         H, G, d = n_head, n_kv, head_dim
         T = batch.n_tokens
+        if partials is not None:
+            qkv = partials.double().sum(0)
         pos, slots = token_positions(batch)
         if int(pos.max()) >= table.shape[0]:
             raise IndexError("position beyond the rotary table")
@@ -115,7 +123,7 @@ class PlainOps:
         out += y.float()
 
     # -- matrix products ---------------------------------------------------------------
-    def linear(self, a, w, out, mode="store"):
+    def linear(self, a, w, out, mode="store", defer=False):
         acc = a.double() @ w.double().T
         if mode == "store":
             out.copy_(acc.to(out.dtype))

@@ -1,0 +1,71 @@
+"""Kernels that finish a sum split over K on their way: RMSNorm with pending
+partial sums, rotary + append from partial sums, the deferred tensor-core product."""
+import math
+
+import pytest
+import torch
+
+from gpt_fast_b200 import ops
+from gpt_fast_b200.ops.types import PagedKV
+import plain_ops
+from test_kernels_gpu import DEV, REF, make_batch, rnd
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T,D,S", [(1, 64, 2), (8, 4096, 8), (5, 144, 3), (64, 1000, 4)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_completes_a_pending_sum(T, D, S, out_dtype):
+    x = rnd(T, D, scale=2.0)
+    pending = rnd(S, T, D, seed=1)
+    w = (1 + 0.1 * rnd(D, seed=2))
+    x_ref = x.clone()
+    out, ref = torch.empty(T, D, dtype=out_dtype, device=DEV), torch.empty(T, D, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, 1e-5, out, None, pending)
+    REF.rmsnorm(x_ref, w, 1e-5, ref, None, pending)
+    torch.testing.assert_close(x, x_ref, rtol=1e-6, atol=1e-6)                       # the residual itself was completed
+    tol = dict(rtol=2e-5, atol=2e-5) if out_dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), ref.float(), **tol)
+    # with a row gather the sum is completed first, for every row
+    x2, x2_ref = rnd(T, D, seed=3), rnd(T, D, seed=3)
+    rows = torch.tensor([T - 1], dtype=torch.int32, device=DEV)
+    o2, r2 = torch.empty(1, D, device=DEV), torch.empty(1, D, device=DEV)
+    ops.rmsnorm(x2, w, 1e-5, o2, rows, pending)
+    REF.rmsnorm(x2_ref, w, 1e-5, r2, rows, pending)
+    torch.testing.assert_close(x2, x2_ref, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(o2, r2, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,q_lens,starts", [(4, 4, 16, [5, 11], [0, 3]), (6, 2, 24, [1, 1, 1], [0, 64, 130]),
+                                                 (32, 8, 128, [1] * 8, [128] * 8)])
+def test_rope_append_from_partial_sums(dtype, H, G, d, q_lens, starts):
+    batch, table, n_pages = make_batch(q_lens, starts, 9, 64, 8)
+    T, W = batch.n_tokens, (H + 2 * G) * d
+    partials = rnd(3, T, W, seed=1)
+    rt = torch.empty(8 * 64, d // 2, 2, device=DEV)
+    ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).to(DEV), rt)
+    pools = [torch.zeros(n_pages, G, 64, d, dtype=dtype, device=DEV) for _ in range(4)]
+    q, q_ref = torch.empty(T, H, d, dtype=dtype, device=DEV), torch.empty(T, H, d, dtype=dtype, device=DEV)
+    unused = torch.empty(T, W, dtype=dtype, device=DEV)
+    ops.rope_append(unused, q, PagedKV(pools[0], pools[1], table, 64), batch, rt, H, G, d, "interleaved", True, partials)
+    REF.rope_append(unused, q_ref, PagedKV(pools[2], pools[3], table, 64), batch, rt, H, G, d, "interleaved", True, partials)
+    ops.check_status(batch.status)
+    tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q.float(), q_ref.float(), **tol)
+    torch.testing.assert_close(pools[0].float(), pools[2].float(), **tol)
+    torch.testing.assert_close(pools[1].float(), pools[3].float(), **tol)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (1, 6144, 4096), (64, 4096, 14336), (16, 512, 1024)])
+def test_deferred_product_leaves_partial_sums(M, N, K):
+    a = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.02, seed=1)
+    x = rnd(M, N, seed=2)
+    ref = x.clone()
+    pending = ops.linear(a, w, x, "add", defer=True)
+    REF.linear(a, w, ref, "add")
+    if pending is not None:
+        assert pending.shape[1:] == (M, N) and pending.shape[0] > 1
+        ops.add_partials(x, pending)
+    torch.testing.assert_close(x, ref, rtol=1e-4, atol=2e-4)

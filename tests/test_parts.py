@@ -12,6 +12,7 @@ from gpt_fast_b200.cache import Cache, CacheNeeds, StateNeed
 from gpt_fast_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from gpt_fast_b200.engine.model import Transformer
 from gpt_fast_b200.ops.types import BatchMeta
+from gpt_fast_b200.parts.residual import Residual
 from gpt_fast_b200.weights.loader import ParamSpec
 import plain_llama
 import plain_ops
@@ -100,7 +101,9 @@ def test_attention_part(backend, dim, H, G, d, S):
     res0 = rnd(S, dim, seed=6)
     residual = res0.clone().to(device)
     batch = one_sequence_batch(cache, S, device)
-    att.forward(h.to(dtype).to(device), batch, cache.view(0), residual)
+    stream = Residual(residual)
+    att.forward(h.to(dtype).to(device), batch, cache.view(0), stream)
+    residual = stream.tensor()
     ops.check_status(batch.status)
     cos, sin = plain_llama.rope_angles(torch.arange(S), plain_llama.rope_frequencies(d, 10000.0))
     want = res0 + plain_llama.attention(h, torch.cat([ws["wq"], ws["wk"], ws["wv"]]), ws["wo"], cos, sin, H, G, d)
@@ -117,7 +120,9 @@ def test_swiglu_part(backend, dim, hidden):
     h = bf16_exact(rnd(11, dim, seed=4))
     res0 = rnd(11, dim, seed=5)
     residual = res0.clone().to(device)
-    ff.forward(h.to(dtype).to(device), residual)
+    stream = Residual(residual)
+    ff.forward(h.to(dtype).to(device), stream)
+    residual = stream.tensor()
     want = res0 + plain_llama.feed_forward(h, ws["w1"], ws["w2"], ws["w3"])
     torch.testing.assert_close(residual.cpu(), want, **tol(dtype))
 
@@ -153,7 +158,7 @@ class RunningMeanMixer:
             if append:
                 view.state[slot] = s
         y = (mixed @ self.w.float().T).to(self.dtype)
-        ops.add_into(residual, y)
+        residual.add(y)
 
 
 def toy_spec(dim=48, vocab=61):
