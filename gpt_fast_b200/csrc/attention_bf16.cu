@@ -27,6 +27,10 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
 
 // q: [T, H, d]; out: [T, H*d]; scratch_o: [T, H, S, d] f32; scratch_ml: [T, H, S, 2] f32
 __global__ void __launch_bounds__(THREADS)
@@ -202,6 +206,193 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     }
 }
 
+// ---- tensor-core version for head_dim 64 and 128 -----------------------------------------
+// The same block structure, but scores and the weighted sum are mma.sync m16n8k16 products:
+// the (up to 8) query heads of the group are rows 0..7 of the 16-row A operand.  Each of the
+// 4 warps owns 16 of a page's 64 keys and runs an online softmax of its own over them (no
+// block-wide exchange per page); the four partial results are merged once at the end.
+// K and V tiles sit in shared memory with rows padded by 16 bytes, so ldmatrix reads them
+// without bank conflicts; V is read with ldmatrix.trans.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// c += a * b with rows 8..15 of a equal to zero (a1 = a3 = 0)
+__device__ __forceinline__ void mma_rows8(float* c, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                       float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
+                       GfbPagedKV kv, GfbBatch b, int H, int G, float scale_log2e, int window, int splits, int* status) {
+    constexpr int PITCH = D + 8;                 // elements per shared-memory row
+    constexpr int KSTEPS = D / 16, NT = D / 8;
+    constexpr int TILE = PAGE * PITCH;           // elements per tile
+    extern __shared__ __align__(16) uint8_t smem[];
+    __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1
+    __nv_bfloat16* qs = tiles + 4 * TILE;                      // [8][PITCH]
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int rep = H / G;
+    const int t = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
+    const int s = b.tok_seq[t];
+    const int slot = b.slots[s];
+    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_page = lo / PAGE, last_page = pos / PAGE;
+    const int n_pages = last_page - first_page + 1;
+    const int per = (n_pages + splits - 1) / splits;
+    const int p0 = first_page + z * per;
+    const int p1 = min(last_page + 1, p0 + per);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gq = lane >> 2, t4 = lane & 3;     // row (head) and column pair of the mma fragments
+
+    for (int i = tid; i < 8 * D; i += THREADS) {
+        int row = i / D, col = i - row * D;
+        qs[row * PITCH + col] = row < rep ? q[((size_t)t * H + g * rep + row) * D + col] : __float2bfloat16_rn(0.f);
+    }
+    const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
+    auto issue = [&](int page_index, int buf) {
+        int page = pt[page_index];
+        if (page < 0 || page >= kv.n_pages) {
+            if (tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, page_index);
+            page = 0;
+        }
+        const __nv_bfloat16* ksrc = (const __nv_bfloat16*)kv.k_pool + ((size_t)page * G + g) * PAGE * D;
+        const __nv_bfloat16* vsrc = (const __nv_bfloat16*)kv.v_pool + ((size_t)page * G + g) * PAGE * D;
+        __nv_bfloat16* kd = tiles + (2 * buf) * TILE;
+        __nv_bfloat16* vd = tiles + (2 * buf + 1) * TILE;
+        for (int c = tid; c < PAGE * (D / 8); c += THREADS) {
+            int row = c / (D / 8), cc = c - row * (D / 8);
+            cp_async16(kd + row * PITCH + cc * 8, ksrc + row * D + cc * 8);
+            cp_async16(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8);
+        }
+    };
+    if (p0 < p1) issue(p0, 0);
+    cp_async_commit();
+    __syncthreads();                                           // qs complete
+
+    uint32_t qa[KSTEPS][2];
+#pragma unroll
+    for (int k = 0; k < KSTEPS; k++) {
+        qa[k][0] = *reinterpret_cast<const uint32_t*>(qs + gq * PITCH + k * 16 + 2 * t4);
+        qa[k][1] = *reinterpret_cast<const uint32_t*>(qs + gq * PITCH + k * 16 + 8 + 2 * t4);
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_run = -INFINITY, l_run = 0.f;
+    const int mid = lane >> 3, mr = lane & 7;                  // ldmatrix: this lane addresses row mr of matrix mid
+
+    for (int p = p0; p < p1; p++) {
+        const int buf = (p - p0) & 1;
+        if (p + 1 < p1) issue(p + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf) * TILE);
+        const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf + 1) * TILE);
+
+        // scores of this warp's 16 keys (two n-tiles of 8) for rows = heads
+        float sc[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; n++) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+#pragma unroll
+        for (int k = 0; k < KSTEPS; k++) {
+            // matrices: (keys 0-7, dims lo), (keys 0-7, dims hi), (keys 8-15, dims lo), (keys 8-15, dims hi)
+            uint32_t addr = kbase + (uint32_t)(((warp * 16 + (mid >> 1) * 8 + mr) * PITCH + k * 16 + (mid & 1) * 8) * 2);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(addr, b0, b1, b2, b3);
+            mma_rows8(sc[0], qa[k][0], qa[k][1], b0, b1);
+            mma_rows8(sc[1], qa[k][0], qa[k][1], b2, b3);
+        }
+        // mask, online softmax over this warp's keys (row = head gq, columns 2*t4, 2*t4+1 of each n-tile)
+        float v[4];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; n++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                int j = p * PAGE + warp * 16 + n * 8 + 2 * t4 + e;
+                float x = (j >= lo && j <= pos) ? sc[n][e] * scale_log2e : -INFINITY;
+                v[n * 2 + e] = x;
+                mx = fmaxf(mx, x);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        float corr = 1.f, pr[4] = {0.f, 0.f, 0.f, 0.f};
+        if (m_new != -INFINITY) {
+            corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+#pragma unroll
+            for (int e = 0; e < 4; e++) pr[e] = (v[e] == -INFINITY) ? 0.f : exp2f(v[e] - m_new);
+        }
+        float rs = pr[0] + pr[1] + pr[2] + pr[3];
+        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+        l_run = l_run * corr + rs;
+        m_run = m_new;
+        const uint32_t pa0 = pack2(pr[0], pr[1]), pa2 = pack2(pr[2], pr[3]);
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            o[j][0] *= corr; o[j][1] *= corr; o[j + 1][0] *= corr; o[j + 1][1] *= corr;
+            // matrices: (keys 0-7, dims j), (keys 8-15, dims j), (keys 0-7, dims j+1), (keys 8-15, dims j+1)
+            uint32_t addr = vbase + (uint32_t)(((warp * 16 + (mid & 1) * 8 + mr) * PITCH + (j + (mid >> 1)) * 8) * 2);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_trans(addr, b0, b1, b2, b3);
+            mma_rows8(o[j], pa0, pa2, b0, b1);
+            mma_rows8(o[j + 1], pa0, pa2, b2, b3);
+        }
+        __syncthreads();                                       // this buffer is refilled next round
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the four warps' partial softmaxes; the tile area is free now
+    float* Ow = (float*)smem;                                  // [4][8][D]
+    float* mw = Ow + 4 * 8 * D;                                // [4][8]
+    float* lw = mw + 32;                                       // [4][8]
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        Ow[(warp * 8 + gq) * D + j * 8 + 2 * t4] = o[j][0];
+        Ow[(warp * 8 + gq) * D + j * 8 + 2 * t4 + 1] = o[j][1];
+    }
+    if (t4 == 0) { mw[warp * 8 + gq] = m_run; lw[warp * 8 + gq] = l_run; }
+    __syncthreads();
+    for (int idx = tid; idx < rep * D; idx += THREADS) {
+        const int h = idx / D, dim = idx - h * D;
+        float m = fmaxf(fmaxf(mw[h], mw[8 + h]), fmaxf(mw[16 + h], mw[24 + h]));
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            float mm = mw[w * 8 + h];
+            if (mm == -INFINITY) continue;
+            float f = exp2f(mm - m);
+            l += lw[w * 8 + h] * f;
+            acc += Ow[(w * 8 + h) * D + dim] * f;
+        }
+        const int head = g * rep + h;
+        if (splits == 1) {
+            out[((size_t)t * H + head) * D + dim] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            scratch_o[(((size_t)t * H + head) * splits + z) * D + dim] = acc;
+            if (dim == 0) {
+                float* ml = scratch_ml + (((size_t)t * H + head) * splits + z) * 2;
+                ml[0] = m;
+                ml[1] = l;
+            }
+        }
+    }
+}
+
 __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
                                     __nv_bfloat16* __restrict__ out, int H, int d, int splits) {
     gfb_pdl_launch();
@@ -253,8 +444,23 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     float* so = scratch;
     float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
     dim3 grid(n_tokens, G, splits);
-    cudaError_t e = gfb_launch(attn_decode_kernel, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
-                               (__nv_bfloat16*)out, so, sml, kv, b, H, G, d, scale * 1.4426950408889634f, window, splits, status);
+    cudaError_t e;
+    if (d == 128 || d == 64) {
+        // tensor-core kernel: 4 padded tiles + the query rows; the merge area reuses the tiles
+        size_t msmem = (size_t)(4 * PAGE + 8) * (d + 8) * 2;
+        static size_t mconf[2] = {0, 0};
+        auto kern = d == 128 ? attn_decode_mma_kernel<128> : attn_decode_mma_kernel<64>;
+        if (msmem > 48 * 1024 && msmem > mconf[d == 128]) {
+            cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem);
+            if (a != cudaSuccess) return gfb_fail("gfb_attn_decode: %zu bytes of shared memory refused: %s", msmem, cudaGetErrorString(a));
+            mconf[d == 128] = msmem;
+        }
+        e = gfb_launch(kern, grid, dim3(THREADS), msmem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b,
+                       H, G, scale * 1.4426950408889634f, window, splits, status);
+    } else {
+        e = gfb_launch(attn_decode_kernel, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
+                       (__nv_bfloat16*)out, so, sml, kv, b, H, G, d, scale * 1.4426950408889634f, window, splits, status);
+    }
     if (gfb_check(e, "gfb_attn_decode")) return 1;
     if (splits > 1) {
         dim3 cgrid(n_tokens, H);

@@ -5,6 +5,8 @@
 // rotation), :97-98 (cache write).  All arithmetic is 32-bit.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 GFB_DEFINE_LAST_ERROR()
 
 // ---------------------------------------------------------------- embedding --
@@ -74,12 +76,71 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_from_f32<TO>(xr[i] * rstd * gfb_to_f32(w[i]));
 }
 
+// The same for few rows: a cluster of NORM_CLUSTER blocks shares one row, so that a decode step's
+// handful of rows keeps many SMs busy; the blocks exchange their sums of squares through
+// distributed shared memory.  Needs D % (4 * NORM_CLUSTER) == 0.
+constexpr int NORM_CLUSTER = 8;
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(128)
+rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending, int S, size_t slice,
+                       const TW* __restrict__ w, TO* __restrict__ out, int D, float eps) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float scratch[32];
+    __shared__ float part;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int r = blockIdx.y;
+    const int chunk = D / NORM_CLUSTER;
+    const int c0 = (int)cluster.block_rank() * chunk;
+    const size_t row = (size_t)r * D;
+    float ss = 0.f;
+    for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
+        float4 v = *reinterpret_cast<const float4*>(x + row + i);
+        if (pending != nullptr) {
+            for (int k = 0; k < S; k++) {
+                float4 p = *reinterpret_cast<const float4*>(pending + (size_t)k * slice + row + i);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            *reinterpret_cast<float4*>(x + row + i) = v;
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = gfb_block_sum(ss, scratch);
+    if (threadIdx.x == 0) part = ss;
+    cluster.sync();
+    float total = 0.f;
+    for (int k = 0; k < NORM_CLUSTER; k++) total += *cluster.map_shared_rank(&part, k);     // fixed order
+    const float rstd = rsqrtf(total / (float)D + eps);
+    for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
+        float4 v = *reinterpret_cast<const float4*>(x + row + i);
+        TO* o = out + row + i;
+        o[0] = gfb_from_f32<TO>(v.x * rstd * gfb_to_f32(w[i]));
+        o[1] = gfb_from_f32<TO>(v.y * rstd * gfb_to_f32(w[i + 1]));
+        o[2] = gfb_from_f32<TO>(v.z * rstd * gfb_to_f32(w[i + 2]));
+        o[3] = gfb_from_f32<TO>(v.w * rstd * gfb_to_f32(w[i + 3]));
+    }
+    cluster.sync();                 // no block leaves while another may still read its `part`
+}
+
 GFB_API int gfb_rmsnorm(float* x, const float* pending, int S, long slice, const void* w, int w_dt, void* out, int out_dt,
                         const int* rows, int R, int D, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (pending != nullptr && rows != nullptr) return gfb_fail("gfb_rmsnorm: pending partial sums cannot be combined with a row gather");
-    int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
     cudaError_t e;
+    if (rows == nullptr && R <= 128 && D >= 1024 && D % (4 * NORM_CLUSTER) == 0) {
+        dim3 grid(NORM_CLUSTER, R);
+#define CLAUNCH(TW, TO) e = gfb_launch_cluster(rmsnorm_cluster_kernel<TW, TO>, grid, dim3(128), 0, stream, NORM_CLUSTER, x, pending, S, (size_t)slice, (const TW*)w, (TO*)out, D, eps)
+        if (w_dt == GFB_BF16 && out_dt == GFB_BF16) CLAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else if (w_dt == GFB_F32 && out_dt == GFB_BF16) CLAUNCH(float, __nv_bfloat16);
+        else if (w_dt == GFB_BF16 && out_dt == GFB_F32) CLAUNCH(__nv_bfloat16, float);
+        else if (w_dt == GFB_F32 && out_dt == GFB_F32) CLAUNCH(float, float);
+        else return gfb_fail("gfb_rmsnorm: unknown types %d %d", w_dt, out_dt);
+#undef CLAUNCH
+        return gfb_check(e, "gfb_rmsnorm (cluster)");
+    }
+    int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
 #define LAUNCH(TW, TO) e = gfb_launch(rmsnorm_kernel<TW, TO>, dim3(R), dim3(threads), 0, stream, x, pending, S, (size_t)slice, (const TW*)w, (TO*)out, rows, D, eps)
     if (w_dt == GFB_BF16 && out_dt == GFB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (w_dt == GFB_F32 && out_dt == GFB_BF16) LAUNCH(float, __nv_bfloat16);

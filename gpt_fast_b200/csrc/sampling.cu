@@ -13,6 +13,8 @@
 // index on ties.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 GFB_DEFINE_LAST_ERROR()
 
 constexpr int THREADS = 512;
@@ -167,10 +169,132 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
     if (threadIdx.x == 0) out[blockIdx.x] = winner == 0x7fffffff ? 0 : winner;
 }
 
+// ---- the same choices with a cluster of blocks per row ---------------------------------------
+// A decode step has few rows and a wide vocabulary: one block per row leaves most of the GPU
+// idle.  Here SAMPLE_CLUSTER blocks share a row.  Each thread keeps its logits in registers
+// (the row is read from memory once); the radix-select histograms and the final candidates are
+// exchanged through distributed shared memory.  The draw itself is the Gumbel form of the
+// exponential race: argmax(p_i / q_i) = argmax(x_i - log q_i), so neither the maximum nor the
+// softmax sum is needed.  Rows wider than SAMPLE_CLUSTER * THREADS * SAMPLE_REGS use the
+// one-block kernels above.
+constexpr int SAMPLE_CLUSTER = 8;
+constexpr int SAMPLE_REGS = 32;
+
+template <bool GREEDY>
+__global__ void __launch_bounds__(THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temp, int top_k,
+                      uint64_t seed, const int64_t* __restrict__ request_ids, const int* __restrict__ token_index,
+                      const int* __restrict__ index_map, float* __restrict__ noise_out) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ unsigned int hist[256];
+    __shared__ unsigned int total[256];
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ float cand_v;
+    __shared__ int cand_i;
+    __shared__ float win_v;
+    __shared__ uint32_t sh_prefix;
+    __shared__ int sh_remaining;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int rowi = blockIdx.y;
+    const int rank = (int)cluster.block_rank();
+    const float* row = logits + (size_t)rowi * V;
+    // element e of this thread: index (e * SAMPLE_CLUSTER + rank) * THREADS + tid  (coalesced per block)
+    float x[SAMPLE_REGS];
+#pragma unroll
+    for (int e = 0; e < SAMPLE_REGS; e++) {
+        int i = (e * SAMPLE_CLUSTER + rank) * THREADS + threadIdx.x;
+        float v = i < V ? row[i] : -INFINITY;
+        if (v != v) v = -INFINITY;
+        x[e] = GREEDY ? v : v / temp;
+    }
+    float pivot = -INFINITY;
+    if (!GREEDY && top_k > 0 && top_k < V) {
+        uint32_t prefix = 0, mask = 0;
+        int remaining = top_k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int i = threadIdx.x; i < 256; i += THREADS) hist[i] = 0;
+            __syncthreads();
+#pragma unroll
+            for (int e = 0; e < SAMPLE_REGS; e++) {
+                int i = (e * SAMPLE_CLUSTER + rank) * THREADS + threadIdx.x;
+                if (i < V) {
+                    uint32_t k = float_key(x[e]);
+                    if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+                }
+            }
+            cluster.sync();                                   // every block's histogram is complete
+            if (threadIdx.x < 256) {
+                unsigned int sum = 0;
+                for (int r = 0; r < SAMPLE_CLUSTER; r++) sum += cluster.map_shared_rank(hist, r)[threadIdx.x];
+                total[threadIdx.x] = sum;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int left = remaining, bin = 255;
+                for (; bin > 0; bin--) {
+                    int c = (int)total[bin];
+                    if (c >= left) break;
+                    left -= c;
+                }
+                sh_prefix = prefix | ((uint32_t)bin << shift);
+                sh_remaining = left;
+            }
+            cluster.sync();                                   // all remote reads of `hist` are done before it is cleared
+            prefix = sh_prefix;
+            remaining = sh_remaining;
+            mask |= 255u << shift;
+        }
+        pivot = key_float(prefix);
+    }
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    if (GREEDY) {
+#pragma unroll
+        for (int e = 0; e < SAMPLE_REGS; e++) {
+            int i = (e * SAMPLE_CLUSTER + rank) * THREADS + threadIdx.x;
+            if (i < V) argmax_combine(best, best_i, x[e], i);
+        }
+    } else {
+        const int64_t request = request_ids ? request_ids[rowi] : (int64_t)rowi;
+        const int tix = token_index ? token_index[index_map ? index_map[rowi] : rowi] : 0;
+#pragma unroll
+        for (int e = 0; e < SAMPLE_REGS; e++) {
+            int i = (e * SAMPLE_CLUSTER + rank) * THREADS + threadIdx.x;
+            if (i < V) {
+                float qn = race_noise(seed, request, tix, i);
+                if (noise_out) noise_out[(size_t)rowi * V + i] = qn;
+                if (x[e] >= pivot) argmax_combine(best, best_i, x[e] - logf(qn), i);
+            }
+        }
+    }
+    int wi = block_argmax(best, best_i, sv, si);
+    if (best_i == wi && wi != 0x7fffffff) win_v = best;       // the thread that holds the block's winner
+    __syncthreads();
+    if (threadIdx.x == 0) { cand_i = wi; cand_v = (wi == 0x7fffffff) ? -INFINITY : win_v; }
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int r = 0; r < SAMPLE_CLUSTER; r++)
+            argmax_combine(bv, bi, *cluster.map_shared_rank(&cand_v, r), *cluster.map_shared_rank(&cand_i, r));
+        out[rowi] = bi == 0x7fffffff ? 0 : bi;
+    }
+    cluster.sync();
+}
+
 GFB_API int gfb_argmax(const float* logits, int* out, int B, int V, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return gfb_fail("gfb_argmax: V = %d", V);
-    cudaError_t e = gfb_launch(argmax_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V);
+    cudaError_t e;
+    if (V <= SAMPLE_CLUSTER * THREADS * SAMPLE_REGS && B <= 65535)
+        e = gfb_launch_cluster(sample_cluster_kernel<true>, dim3(SAMPLE_CLUSTER, B), dim3(THREADS), 0, stream, SAMPLE_CLUSTER,
+                               logits, out, V, 1.0f, 0, (uint64_t)0, (const int64_t*)nullptr, (const int*)nullptr,
+                               (const int*)nullptr, (float*)nullptr);
+    else
+        e = gfb_launch(argmax_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V);
     return gfb_check(e, "gfb_argmax");
 }
 
@@ -180,7 +304,13 @@ GFB_API int gfb_sample(const float* logits, int* out, int B, int V, float temper
     if (B <= 0) return 0;
     if (V <= 0) return gfb_fail("gfb_sample: V = %d", V);
     float t = temperature > 1e-5f ? temperature : 1e-5f;
-    cudaError_t e = gfb_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V, t, top_k, (uint64_t)seed,
-                               (const int64_t*)request_ids, token_index, index_map, noise_out);
+    cudaError_t e;
+    if (V <= SAMPLE_CLUSTER * THREADS * SAMPLE_REGS && B <= 65535)
+        e = gfb_launch_cluster(sample_cluster_kernel<false>, dim3(SAMPLE_CLUSTER, B), dim3(THREADS), 0, stream, SAMPLE_CLUSTER,
+                               logits, out, V, t, top_k, (uint64_t)seed, (const int64_t*)request_ids, token_index, index_map,
+                               noise_out);
+    else
+        e = gfb_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V, t, top_k, (uint64_t)seed,
+                       (const int64_t*)request_ids, token_index, index_map, noise_out);
     return gfb_check(e, "gfb_sample");
 }

@@ -125,7 +125,8 @@ class DecodeBatch:
         self.batch = BatchMeta(cu_seqlens=ar.to(dev), tok_seq=ar[:n].to(dev),
                                slots=torch.tensor(self.slots, dtype=torch.int32).to(dev),
                                lengths=self.cache.lengths, n_seqs=n, n_tokens=n, max_q_len=1,
-                               max_kv_len=self.cache.max_seq_len, status=stepper.status)
+                               max_kv_len=max([self.cache.reserved_host[s] for s in self.slots] + [self.cache.page_size]),
+                               status=stepper.status)
         self.sampler = sampler
         self.logits = None
         self.use_graph = use_graph and dev.type == "cuda"
