@@ -141,53 +141,90 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// ---- epilogues --------------------------------------------------------------------
-// normal orientation: this thread owns output row `m` (a token), v = 16 consecutive columns n..n+15
-template <int EPI, typename TO>
-__device__ __forceinline__ void epilogue_row(const float* v, TO* out, int m, int n, int N, int ldo) {
-    if (EPI == EPI_SWIGLU) {
-        // pairs (gate, up) -> 8 outputs at columns n/2 ..
-        __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)m * ldo + (n >> 1);
-        if (n + 16 <= N) {
-            uint4 pk;
-            pk.x = pack_bf16(silu_mul(v[0], v[1]), silu_mul(v[2], v[3]));
-            pk.y = pack_bf16(silu_mul(v[4], v[5]), silu_mul(v[6], v[7]));
-            pk.z = pack_bf16(silu_mul(v[8], v[9]), silu_mul(v[10], v[11]));
-            pk.w = pack_bf16(silu_mul(v[12], v[13]), silu_mul(v[14], v[15]));
-            *reinterpret_cast<uint4*>(o) = pk;
-        } else {
-            for (int j = 0; j + 1 < 16 && n + j + 1 < N; j += 2) o[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
-        }
-    } else if (EPI == EPI_ADD) {
-        float* o = (float*)out + (size_t)m * ldo + n;
-        if (n + 16 <= N) {
+// ---- epilogue of the normal orientation -------------------------------------------------
+// The accumulator has one row (token) per thread, which would make every global access a
+// 32-row gather.  So each epilogue warp first copies its 32 accumulator rows from tensor memory
+// to shared memory (the ring is free by then; rows padded by 4 floats so the copies do not
+// collide on banks), then walks ITS rows with all lanes side by side along a row: global reads
+// and writes are whole contiguous lines, and the residual loads of four rows are in flight
+// together.  Only __syncwarp is needed: a warp reads back what it wrote itself.
+template <int BN, int EPI, typename TO>
+__device__ __forceinline__ void epilogue_rows(float* stage, uint32_t taddr, int q, int lane, TO* out, int row0, int col0,
+                                              int R, int N, int ldo) {
+    constexpr int SP = BN + 4;
+    float* mine = stage + (size_t)(q * 32 + lane) * SP;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tmem_ld16(taddr + c, v);
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-                float4 x = *reinterpret_cast<float4*>(o + j);
-                x.x += v[j]; x.y += v[j + 1]; x.z += v[j + 2]; x.w += v[j + 3];
-                *reinterpret_cast<float4*>(o + j) = x;
+        for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(mine + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+    __syncwarp();
+    const int rows = min(32, R - (row0 + q * 32));
+    if (EPI == EPI_ADD) {
+        constexpr int PASSES = BN >= 128 ? BN / 128 : 1;        // 32 lanes x float4 = 128 columns per pass
+#pragma unroll 1
+        for (int rr = 0; rr < rows; rr += 4) {
+            float4 res[4][PASSES];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int ps = 0; ps < PASSES; ps++) {
+                    int col = col0 + ps * 128 + lane * 4;
+                    if (rr + u < rows && col < N)
+                        res[u][ps] = *reinterpret_cast<const float4*>((float*)out + (size_t)(row0 + q * 32 + rr + u) * ldo + col);
+                }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int ps = 0; ps < PASSES; ps++) {
+                    int col = col0 + ps * 128 + lane * 4;
+                    if (rr + u < rows && col < N) {
+                        float4 a = *reinterpret_cast<const float4*>(stage + (size_t)(q * 32 + rr + u) * SP + ps * 128 + lane * 4);
+                        float4 x = res[u][ps];
+                        x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w;
+                        *reinterpret_cast<float4*>((float*)out + (size_t)(row0 + q * 32 + rr + u) * ldo + col) = x;
+                    }
+                }
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        // 8 accumulator columns (4 gate/up pairs) per lane -> 4 outputs
+#pragma unroll 2
+        for (int rr = 0; rr < rows; rr++) {
+            int c = lane * 8;
+            if (c < BN && col0 + c < N) {
+                const float* a = stage + (size_t)(q * 32 + rr) * SP + c;
+                float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
+                uint2 pk;
+                pk.x = pack_bf16(silu_mul(lo.x, lo.y), silu_mul(lo.z, lo.w));
+                pk.y = pack_bf16(silu_mul(hi.x, hi.y), silu_mul(hi.z, hi.w));
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)(row0 + q * 32 + rr) * ldo + ((col0 + c) >> 1)) = pk;
             }
-        } else {
-            for (int j = 0; j < 16 && n + j < N; j++) o[j] += v[j];
         }
     } else if (sizeof(TO) == 4) {
-        float* o = (float*)out + (size_t)m * ldo + n;
-        if (n + 16 <= N) {
+        constexpr int PASSES = BN >= 128 ? BN / 128 : 1;
+#pragma unroll 2
+        for (int rr = 0; rr < rows; rr++)
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-            for (int j = 0; j < 16 && n + j < N; j++) o[j] = v[j];
-        }
+            for (int ps = 0; ps < PASSES; ps++) {
+                int c = ps * 128 + lane * 4;
+                if (col0 + c < N)
+                    *reinterpret_cast<float4*>((float*)out + (size_t)(row0 + q * 32 + rr) * ldo + col0 + c) =
+                        *reinterpret_cast<const float4*>(stage + (size_t)(q * 32 + rr) * SP + c);
+            }
     } else {
-        __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)m * ldo + n;
-        if (n + 16 <= N) {
-            uint4 a, b;
-            a.x = pack_bf16(v[0], v[1]); a.y = pack_bf16(v[2], v[3]); a.z = pack_bf16(v[4], v[5]); a.w = pack_bf16(v[6], v[7]);
-            b.x = pack_bf16(v[8], v[9]); b.y = pack_bf16(v[10], v[11]); b.z = pack_bf16(v[12], v[13]); b.w = pack_bf16(v[14], v[15]);
-            *reinterpret_cast<uint4*>(o) = a;
-            *reinterpret_cast<uint4*>(o + 8) = b;
-        } else {
-            for (int j = 0; j < 16 && n + j < N; j++) o[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll 2
+        for (int rr = 0; rr < rows; rr++) {
+            int c = lane * 8;
+            if (c < BN && col0 + c < N) {
+                const float* a = stage + (size_t)(q * 32 + rr) * SP + c;
+                float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
+                uint4 pk;
+                pk.x = pack_bf16(lo.x, lo.y); pk.y = pack_bf16(lo.z, lo.w);
+                pk.z = pack_bf16(hi.x, hi.y); pk.w = pack_bf16(hi.z, hi.w);
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)out + (size_t)(row0 + q * 32 + rr) * ldo + col0 + c) = pk;
+            }
         }
     }
 }
@@ -292,14 +329,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tc_fence_after();
         if (ok) {
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
+            if constexpr (!SWAP) {
+                if (row0 + q * 32 < R)
+                    epilogue_rows<BN, EPI == EPI_PARTIAL ? EPI_STORE : EPI, TO>(reinterpret_cast<float*>(aligned), taddr, q, lane,
+                                                                                out, row0, col0, R, Cc, ldo);
+            } else {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 if (col0 + c >= Cc) break;                  // uniform: nothing left in this tile
                 float v[16];
                 tmem_ld16(taddr + c, v);
-                if (!SWAP) {
-                    if (r < R) epilogue_row<EPI, TO>(v, out, r, col0 + c, Cc, ldo);
-                } else {
+                {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         int m = col0 + c + j;               // token
@@ -316,6 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         }
                     }
                 }
+            }
             }
         }
     }
@@ -397,6 +438,8 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 size_t smem_bytes(int bn, int stages) {
     return 1024 + (size_t)stages * (X_TILE_BYTES + bn * BK * 2) + sizeof(Barriers);
 }
+// the normal orientation stages its 128 x bn accumulator (rows padded by 4 floats) in the ring
+size_t staging_bytes(int bn) { return (size_t)BM * (bn + 4) * 4; }
 
 template <int BN, bool SWAP, int EPI, typename TO>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, int R, int Cc, int K, int ldo,
@@ -446,6 +489,8 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc: operands must be 16-byte aligned");
     if (stages < 2 || stages > MAX_STAGES) return gfb_fail("gfb_gemm_tc: stages = %d out of range", stages);
     if (smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
+    if (!swap && (size_t)stages * (X_TILE_BYTES + bn * BK * 2) < staging_bytes(bn))
+        return gfb_fail("gfb_gemm_tc: %d stages are too few to stage a 128 x %d accumulator", stages, bn);
     const int total_kb = (K + BK - 1) / BK;
     if (splits < 1) splits = 1;
     if (splits > total_kb) splits = total_kb;

@@ -225,8 +225,15 @@ class CudaKernels:
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim),
                    c_float(scale), c_int(window or 0), _ptr(batch.status), _stream())
 
-    def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None):
+    def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None):
         T = batch.n_tokens
+        if prefill is None:
+            prefill = splits is None and batch.max_q_len > 1 and head_dim in (64, 128)
+        if prefill:
+            self._call("attention_bf16", "gfb_attn_prefill", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                       c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0),
+                       _ptr(batch.status), _stream())
+            return
         if splits is None:
             splits = 1
             if batch.max_q_len == 1:       # decode: slice long sequences until about two blocks per SM work

@@ -69,3 +69,49 @@ def test_deferred_product_leaves_partial_sums(M, N, K):
         assert pending.shape[1:] == (M, N) and pending.shape[0] > 1
         ops.add_partials(x, pending)
     torch.testing.assert_close(x, ref, rtol=1e-4, atol=2e-4)
+
+
+PREFILL_CASES = [  # H, G, d, q_lens, starts
+    (32, 8, 128, [130, 1, 70], [0, 300, 30]),
+    (8, 1, 64, [17, 200], [63, 0]),
+    (6, 2, 64, [45, 3, 129], [5, 64, 100]),           # 3 heads per group: 42 tokens per tile, 2 idle rows
+    (5, 5, 128, [260], [0]),                          # one head per group: 128 tokens per tile
+    (16, 2, 128, [33, 64], [1000, 7]),                # 8 heads per group
+]
+
+
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("H,G,d,q_lens,starts", PREFILL_CASES)
+def test_attention_bf16_prefill(window, H, G, d, q_lens, starts):
+    batch, table, n_pages = make_batch(q_lens, starts, 5, 64, 24, seed=3)
+    T, dt = batch.n_tokens, torch.bfloat16
+    kv = PagedKV(rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5), table, 64)
+    q = rnd(T, H, d, dtype=dt, seed=6)
+    out, ref = torch.empty(T, H * d, dtype=dt, device=DEV), torch.empty(T, H * d, dtype=dt, device=DEV)
+    ops.attention(q, kv, batch, out, H, G, d, 1 / math.sqrt(d), window)
+    REF.attention(q, kv, batch, ref, H, G, d, 1 / math.sqrt(d), window)
+    ops.check_status(batch.status)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
+
+
+def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal():
+    """A key far back dominates every later query; a key made huge at position p must not leak into queries before p."""
+    H, G, d = 8, 2, 128
+    batch, table, n_pages = make_batch([300], [0], 2, 64, 8, seed=9)
+    dt = torch.bfloat16
+    k = rnd(n_pages, G, 64, d, dtype=dt, scale=0.1, seed=1)
+    v = rnd(n_pages, G, 64, d, dtype=dt, seed=2)
+    q = rnd(300, H, d, dtype=dt, scale=0.1, seed=3)
+    slot = int(batch.slots[0])
+    q[:, :, 0] = 30.0
+    for pos in (3, 200):
+        k[int(table[slot, pos // 64]), :, pos % 64, 0] = 30.0 if pos == 3 else 60.0
+    kv = PagedKV(k, v, table, 64)
+    out = torch.empty(300, H * d, dtype=dt, device=DEV)
+    ops.attention(q, kv, batch, out, H, G, d, 1.0, None)
+    v3 = v[int(table[slot, 0]), :, 3].repeat_interleave(H // G, dim=0).reshape(H * d).float()
+    v200 = v[int(table[slot, 200 // 64]), :, 200 % 64].repeat_interleave(H // G, dim=0).reshape(H * d).float()
+    for t in (3, 64, 199):
+        torch.testing.assert_close(out[t].float(), v3, rtol=1e-2, atol=1e-2)
+    for t in (200, 299):
+        torch.testing.assert_close(out[t].float(), v200, rtol=1e-2, atol=1e-2)
