@@ -374,6 +374,244 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
 }
 
+// ---- persistent kernel for many tokens ---------------------------------------------------------
+// One block per SM walks over 128 x 256 output tiles (row tiles fastest, so that the blocks
+// running together share a few weight tiles and all of the activations in L2).  Tensor memory
+// holds TWO accumulators: while the epilogue warps drain tile i (tensor memory -> a small
+// per-warp staging area in shared memory -> coalesced global accesses), the MMA warp already
+// fills the other accumulator with tile i+1, fed by the same TMA ring, whose stage and phase
+// counters simply run on across tiles.
+struct PBarriers {
+    unsigned long long full[MAX_STAGES];
+    unsigned long long empty[MAX_STAGES];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr int PBN = 256;                 // tile width
+constexpr int PCW = 32;                  // columns staged at a time
+constexpr int PSP = PCW + 4;             // staging row pitch in floats
+constexpr int P_STAGING_BYTES = 4 * 32 * PSP * 4;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// drain PCW accumulator columns [c0, c0+PCW) of this warp's 32 rows and apply the epilogue
+template <int EPI, typename TO>
+__device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0, int lane, TO* out, int grow0, int gcol0,
+                                            int rows, int N, int ldo) {
+    float* mine = stage + lane * PSP;
+#pragma unroll
+    for (int c = 0; c < PCW; c += 16) {
+        float v[16];
+        tmem_ld16(taddr + c0 + c, v);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(mine + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+    __syncwarp();
+    const int gc = gcol0 + c0;
+    if (EPI == EPI_ADD || (EPI == EPI_STORE && sizeof(TO) == 4)) {
+        // PCW/4 lanes x float4 cover a row's columns: RPI rows per instruction, 4 x RPI rows in flight
+        constexpr int LPR = PCW / 4, RPI = 32 / LPR;
+        const int sub = lane / LPR, col = (lane % LPR) * 4;
+#pragma unroll 1
+        for (int rr = 0; rr < rows; rr += 4 * RPI) {
+            float4 res[4];
+            if (EPI == EPI_ADD) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    int r = rr + RPI * u + sub;
+                    if (r < rows && gc + col < N) res[u] = *reinterpret_cast<const float4*>((float*)out + (size_t)(grow0 + r) * ldo + gc + col);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                int r = rr + RPI * u + sub;
+                if (r < rows && gc + col < N) {
+                    float4 a = *reinterpret_cast<const float4*>(stage + r * PSP + col);
+                    if (EPI == EPI_ADD) { a.x += res[u].x; a.y += res[u].y; a.z += res[u].z; a.w += res[u].w; }
+                    *reinterpret_cast<float4*>((float*)out + (size_t)(grow0 + r) * ldo + gc + col) = a;
+                }
+            }
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        // PCW/8 lanes x 8 accumulator columns (4 gate/up pairs -> 4 outputs) cover a row
+        constexpr int LPR = PCW / 8, RPI = 32 / LPR;
+        const int sub = lane / LPR, col = (lane % LPR) * 8;
+#pragma unroll 2
+        for (int rr = 0; rr < rows; rr += RPI) {
+            int r = rr + sub;
+            if (r < rows && gc + col < N) {
+                const float* a = stage + r * PSP + col;
+                float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
+                uint2 pk;
+                pk.x = pack_bf16(silu_mul(lo.x, lo.y), silu_mul(lo.z, lo.w));
+                pk.y = pack_bf16(silu_mul(hi.x, hi.y), silu_mul(hi.z, hi.w));
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)(grow0 + r) * ldo + ((gc + col) >> 1)) = pk;
+            }
+        }
+    } else {
+        constexpr int LPR = PCW / 8, RPI = 32 / LPR;
+        const int sub = lane / LPR, col = (lane % LPR) * 8;
+#pragma unroll 2
+        for (int rr = 0; rr < rows; rr += RPI) {
+            int r = rr + sub;
+            if (r < rows && gc + col < N) {
+                const float* a = stage + r * PSP + col;
+                float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
+                uint4 pk;
+                pk.x = pack_bf16(lo.x, lo.y); pk.y = pack_bf16(lo.z, lo.w);
+                pk.z = pack_bf16(hi.x, hi.y); pk.w = pack_bf16(hi.z, hi.w);
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)out + (size_t)(grow0 + r) * ldo + gc + col) = pk;
+            }
+        }
+    }
+    __syncwarp();                      // the staging rows are rewritten by the next chunk
+}
+
+template <int EPI, typename TO>
+__global__ void __launch_bounds__(192)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                          TO* __restrict__ out, int R, int Cc, int K, int ldo, int stages, int* status) {
+    constexpr int Y_TILE_BYTES = PBN * BK * 2;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t xs = base;
+    const uint32_t ys = base + (uint32_t)stages * X_TILE_BYTES;
+    float* staging = reinterpret_cast<float*>(aligned + (size_t)stages * (X_TILE_BYTES + Y_TILE_BYTES));
+    PBarriers* bars = reinterpret_cast<PBarriers*>(aligned + (size_t)stages * (X_TILE_BYTES + Y_TILE_BYTES) + P_STAGING_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_tiles = (R + BM - 1) / BM, col_tiles = (Cc + PBN - 1) / PBN;
+    const int n_tiles = row_tiles * col_tiles;
+    const int nkb = (K + BK - 1) / BK;
+    const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(smem_u32(&bars->acc_full[a]), 1);
+            mbar_init(smem_u32(&bars->acc_empty[a]), 4);       // one arrival per epilogue warp
+        }
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    gfb_pdl_launch();
+    if (!(warp == 0 && lane == 0)) gfb_pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const long total = (long)my_tiles * nkb;
+            auto coords = [&](long it, int& kb, int& row0, int& col0) {
+                const int ti = (int)(it / nkb);
+                kb = (int)(it - (long)ti * nkb);
+                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+                row0 = (tile % row_tiles) * BM;
+                col0 = (tile / row_tiles) * PBN;
+            };
+            // prime the ring with weight tiles (no kernel writes weights), then wait for the
+            // previous kernel and add the activation tiles of the same stages
+            const long n_pre = total < (long)stages ? total : (long)stages;
+            int kb, row0, col0;
+            for (long it = 0; it < n_pre; it++) {
+                coords(it, kb, row0, col0);
+                const uint32_t full = smem_u32(&bars->full[it]);
+                mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                tma_load_2d(ys + (int)it * Y_TILE_BYTES, &map_y, kb * BK, col0, full);
+            }
+            gfb_pdl_wait();
+            for (long it = 0; it < n_pre; it++) {
+                coords(it, kb, row0, col0);
+                tma_load_2d(xs + (int)it * X_TILE_BYTES, &map_x, kb * BK, row0, smem_u32(&bars->full[it]));
+            }
+            for (long it = n_pre; it < total; it++) {
+                coords(it, kb, row0, col0);
+                const int s = (int)(it % stages);
+                const uint32_t ph = (uint32_t)(it / stages) & 1u;
+                if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+                const uint32_t full = smem_u32(&bars->full[s]);
+                mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                tma_load_2d(xs + s * X_TILE_BYTES, &map_x, kb * BK, row0, full);
+                tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, kb * BK, col0, full);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BM, PBN);
+            long it = 0;
+            bool ok = true;
+            for (int ti = 0; ti < my_tiles && ok; ti++) {
+                const int ab = ti & 1;
+                ok = mbar_wait(smem_u32(&bars->acc_empty[ab]), ((uint32_t)(ti >> 1) & 1u) ^ 1u, abort_flag, status, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)(ab * PBN);
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = (int)(it % stages);
+                    const uint32_t ph = (uint32_t)(it / stages) & 1u;
+                    ok = mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag, status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = umma_smem_desc(xs + s * X_TILE_BYTES);
+                    const uint64_t db = umma_smem_desc(ys + s * Y_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit(smem_u32(&bars->empty[s]));
+                }
+                if (ok) umma_commit(smem_u32(&bars->acc_full[ab]));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        float* stage = staging + q * 32 * PSP;
+        for (int ti = 0; ti < my_tiles; ti++) {
+            const int ab = ti & 1;
+            const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+            const int row0 = (tile % row_tiles) * BM, col0 = (tile / row_tiles) * PBN;
+            if (!mbar_wait(smem_u32(&bars->acc_full[ab]), (uint32_t)(ti >> 1) & 1u, abort_flag, status, 3)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * PBN);
+            const int rows = min(32, R - (row0 + q * 32));
+#pragma unroll 1
+            for (int c0 = 0; c0 < PBN; c0 += PCW) {
+                if (col0 + c0 >= Cc) break;
+                if (rows > 0) drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo);
+                else { float v[16]; for (int c = 0; c < PCW; c += 16) tmem_ld16(taddr + c0 + c, v); }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[ab]));
+        }
+    }
+
+    if (*abort_flag) {
+        unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 50000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // Sum the partials of a split over K in ascending split order and apply the epilogue.
 // partial: [S][M][N] f32.
 template <int EPI, typename TO>
@@ -457,6 +695,27 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* parti
     return gfb_check(e, "gfb_gemm_tc");
 }
 
+size_t persistent_smem_bytes(int stages) {
+    return 1024 + (size_t)stages * (X_TILE_BYTES + PBN * BK * 2) + P_STAGING_BYTES + sizeof(PBarriers);
+}
+
+template <int EPI, typename TO>
+int launch_persistent(const CUtensorMap& mx, const CUtensorMap& my, void* out, int R, int Cc, int K, int ldo, int stages,
+                      int sm_count, int* status, cudaStream_t stream) {
+    auto kern = gemm_tc_persistent_kernel<EPI, TO>;
+    size_t smem = persistent_smem_bytes(stages);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gfb_fail("gfb_gemm_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = smem;
+    }
+    int tiles = ((R + BM - 1) / BM) * ((Cc + PBN - 1) / PBN);
+    dim3 grid(tiles < sm_count ? tiles : sm_count);
+    cudaError_t e = gfb_launch(kern, grid, dim3(192), smem, stream, mx, my, (TO*)out, R, Cc, K, ldo, stages, status);
+    return gfb_check(e, "gfb_gemm_tc (persistent)");
+}
+
 template <int BN, bool SWAP>
 int dispatch_epi(int epi, int out_dt, const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, int R,
                  int Cc, int K, int ldo, int splits, int kbps, int stages, int* status, cudaStream_t stream) {
@@ -488,8 +747,8 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     if (epi == EPI_SWIGLU && N % 16) return gfb_fail("gfb_gemm_tc: SwiGLU needs N %% 16 == 0, got %d", N);
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc: operands must be 16-byte aligned");
     if (stages < 2 || stages > MAX_STAGES) return gfb_fail("gfb_gemm_tc: stages = %d out of range", stages);
-    if (smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
-    if (!swap && (size_t)stages * (X_TILE_BYTES + bn * BK * 2) < staging_bytes(bn))
+    if (bn != 512 && smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
+    if (!swap && bn != 512 && (size_t)stages * (X_TILE_BYTES + bn * BK * 2) < staging_bytes(bn))
         return gfb_fail("gfb_gemm_tc: %d stages are too few to stage a 128 x %d accumulator", stages, bn);
     const int total_kb = (K + BK - 1) / BK;
     if (splits < 1) splits = 1;
@@ -504,9 +763,27 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     const int R = swap ? N : M, Cc = swap ? M : N;
     CUtensorMap mx, my;
     if (make_map(&mx, swap ? W : A, R, K, BM)) return 1;
-    if (make_map(&my, swap ? A : W, Cc, K, bn)) return 1;
+    if (make_map(&my, swap ? A : W, Cc, K, bn == 512 ? PBN : bn)) return 1;
     const int kernel_epi = splits > 1 ? EPI_PARTIAL : epi;
     int rc;
+    if (!swap && bn == 512) {
+        // persistent kernel: 128 x 256 tiles, two accumulators in tensor memory
+        static int sm_count = 0;
+        if (sm_count == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        }
+        int st = stages;
+        while (st > 2 && persistent_smem_bytes(st) > 227 * 1024) st--;
+        CUtensorMap my2;
+        if (make_map(&my2, W, N, K, PBN)) return 1;
+        typedef __nv_bfloat16 bf16;
+        if (epi == EPI_ADD) return launch_persistent<EPI_ADD, float>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
+        if (epi == EPI_SWIGLU) return launch_persistent<EPI_SWIGLU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
+        if (out_dt == GFB_F32) return launch_persistent<EPI_STORE, float>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
+        return launch_persistent<EPI_STORE, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
+    }
 #define BNCASE(B, S) rc = dispatch_epi<B, S>(kernel_epi, out_dt, mx, my, out, workspace, R, Cc, K, ldo, splits, kbps, stages, status, stream)
     if (!swap && bn == 256) BNCASE(256, false);
     else if (!swap && bn == 128) BNCASE(128, false);

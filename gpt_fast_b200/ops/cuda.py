@@ -183,8 +183,12 @@ class CudaKernels:
             stage = 16384 + bn * 128
             stages = max(2, min(8, (100 * 1024) // stage))
             return 1, bn, splits, stages
-        bn = 256 if N >= 256 else 128
-        return 0, bn, 1, 4 if bn == 256 else 6
+        if N >= 256:
+            tiles = -(-M // 128) * -(-N // 256)
+            # many tiles per SM: the persistent kernel (bn 512 = 128 x 256 tiles, two accumulators, the
+            # epilogue hidden behind the next tile); few: one tile per block
+            return 0, (512 if tiles >= 4 * self.sm_count else 256), 1, 4
+        return 0, 128, 1, 6
 
     @property
     def sm_count(self):

@@ -299,7 +299,7 @@ def test_sample_frequencies_follow_softmax():
 
 # ---- tensor-core product (tcgen05 + TMA) -------------------------------------------------
 TC_SHAPES = [(1, 384, 144), (8, 512, 256), (5, 320, 144), (16, 1024, 4096), (17, 6144, 512), (64, 768, 2048),
-             (100, 1008, 200), (128, 256, 64), (129, 512, 1024), (300, 640, 456), (256, 2048, 4096)]
+             (100, 1008, 200), (128, 256, 64), (129, 512, 1024), (300, 640, 456), (256, 2048, 4096), (1000, 4352, 512), (2048, 1024, 1024)]
 
 
 @pytest.mark.parametrize("mode", ["store", "store32", "add", "swiglu"])
@@ -327,7 +327,7 @@ def test_linear_tensor_core(mode, M, N, K):
 
 
 @pytest.mark.parametrize("swap,bn,splits,stages", [(1, 16, 1, 2), (1, 16, 3, 6), (1, 32, 2, 4), (1, 64, 5, 3), (1, 128, 1, 4),
-                                                   (1, 128, 4, 3), (0, 128, 1, 3), (0, 128, 1, 6), (0, 256, 1, 4), (0, 256, 1, 3)])
+                                                   (1, 128, 4, 3), (0, 128, 1, 3), (0, 128, 1, 6), (0, 256, 1, 4), (0, 256, 1, 3), (0, 512, 1, 4), (0, 512, 1, 2)])
 @pytest.mark.parametrize("mode", ["store", "add", "swiglu"])
 def test_tensor_core_plans(swap, bn, splits, stages, mode):
     """Every orientation, tile width, split and ring depth gives the same product."""
