@@ -1,0 +1,123 @@
+"""Times single kernels of the library at given sizes (CUDA events around a
+CUDA graph of repeated launches, so that host time is not measured), and is
+the small, self-ending workload that profiler captures are taken on.
+
+    python -m gpt_fast_b200.engine.kernel_bench linear --m 8 --n 28672 --k 4096 --mode swiglu
+    python -m gpt_fast_b200.engine.kernel_bench linear --m 2048 --n 6144 --k 4096 --mode store
+    python -m gpt_fast_b200.engine.kernel_bench attention --batch 8 --context 4000
+    python -m gpt_fast_b200.engine.kernel_bench attention --batch 1 --context 0 --new 2048
+    python -m gpt_fast_b200.engine.kernel_bench sample --batch 8 --vocab 128256
+
+Weights are cycled through enough copies to exceed the L2 cache, so a memory-
+bound kernel is timed against DRAM.  gpt-fast has no per-kernel timing; its
+`--profile` exports a torch profiler trace of one sample (generate.py:380-407).
+"""
+import argparse
+import math
+import sys
+
+import torch
+
+from .. import ops
+from ..ops.types import BatchMeta, PagedKV
+
+L2_BYTES = 126e6
+
+
+def graph_time_us(fn, reps, warm=2):
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(reps):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def bench_linear(a):
+    M, N, K = a.m, a.n, a.k
+    copies = max(2, int(3 * L2_BYTES // (N * K * 2)) + 1) if M <= 128 else 1
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out_dtype = torch.float32 if a.mode == "add" else torch.bfloat16
+    out = torch.zeros(M, N // 2 if a.mode == "swiglu" else N, device="cuda", dtype=out_dtype)
+    us = graph_time_us(lambda i: ops.linear(x, ws[i % copies], out, a.mode, defer=a.mode != "swiglu"), a.reps)
+    gbs = N * K * 2 / us / 1e3
+    tfs = 2.0 * M * N * K / us / 1e6
+    print(f"linear M={M} N={N} K={K} mode={a.mode}: {us:.1f} us, weights at {gbs:.0f} GB/s, {tfs:.0f} TFLOP/s "
+          f"(plan swap,bn,splits,stages = {ops.kernels().tc_plan(M, N, K)})")
+
+
+def paged_batch(batch, context, new, heads_kv, head_dim, device="cuda"):
+    """`batch` sequences with `context` cached tokens each, bringing `new` tokens; pages in shuffled order."""
+    total = context + new
+    pages_each = -(-total // 64)
+    n_pages = batch * pages_each
+    perm = torch.randperm(n_pages).to(torch.int32).view(batch, pages_each)
+    table = perm.to(device)
+    cu = torch.arange(batch + 1, dtype=torch.int32) * new
+    meta = BatchMeta(cu.to(device), torch.arange(batch, dtype=torch.int32).repeat_interleave(new).to(device),
+                     torch.arange(batch, dtype=torch.int32).to(device),
+                     torch.full((batch,), context, dtype=torch.int32, device=device), batch, batch * new, new, total,
+                     ops.new_status(device))
+    k = torch.randn(n_pages, heads_kv, 64, head_dim, device=device, dtype=torch.bfloat16)
+    v = torch.randn(n_pages, heads_kv, 64, head_dim, device=device, dtype=torch.bfloat16)
+    return meta, PagedKV(k, v, table, 64)
+
+
+def bench_attention(a):
+    H, G, d = a.heads, a.kv_heads, a.head_dim
+    meta, kv = paged_batch(a.batch, a.context, a.new, G, d)
+    q = torch.randn(meta.n_tokens, H, d, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(meta.n_tokens, H * d, device="cuda", dtype=torch.bfloat16)
+    us = graph_time_us(lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d)), a.reps)
+    kv_bytes = a.batch * (a.context + a.new) * G * d * 2 * 2
+    if a.new == 1:
+        print(f"attention decode batch={a.batch} context={a.context}: {us:.1f} us, K/V at {kv_bytes / us / 1e3:.0f} GB/s")
+    else:
+        T0, T1 = a.context, a.context + a.new
+        flops = a.batch * 4.0 * H * d * (T1 * (T1 + 1) / 2 - T0 * (T0 + 1) / 2)
+        print(f"attention prefill batch={a.batch} context={a.context} new={a.new}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+    ops.check_status(meta.status)
+
+
+def bench_sample(a):
+    logits = torch.randn(a.batch, a.vocab, device="cuda")
+    tok = torch.empty(a.batch, dtype=torch.int32, device="cuda")
+    us = graph_time_us(lambda i: ops.sample(logits, tok, 0.8, a.top_k or None, 1), a.reps)
+    print(f"sample batch={a.batch} vocab={a.vocab} top_k={a.top_k}: {us:.1f} us")
+    us = graph_time_us(lambda i: ops.argmax(logits, tok), a.reps)
+    print(f"argmax batch={a.batch} vocab={a.vocab}: {us:.1f} us")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="kernel_bench")
+    sub = ap.add_subparsers(dest="what", required=True)
+    p = sub.add_parser("linear")
+    p.add_argument("--m", type=int, default=8); p.add_argument("--n", type=int, default=28672)
+    p.add_argument("--k", type=int, default=4096); p.add_argument("--mode", default="swiglu", choices=["store", "add", "swiglu"])
+    p.add_argument("--reps", type=int, default=10)
+    p = sub.add_parser("attention")
+    p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=4000)
+    p.add_argument("--new", type=int, default=1); p.add_argument("--heads", type=int, default=32)
+    p.add_argument("--kv_heads", type=int, default=8); p.add_argument("--head_dim", type=int, default=128)
+    p.add_argument("--reps", type=int, default=10)
+    p = sub.add_parser("sample")
+    p.add_argument("--batch", type=int, default=8); p.add_argument("--vocab", type=int, default=128256)
+    p.add_argument("--top_k", type=int, default=200); p.add_argument("--reps", type=int, default=10)
+    a = ap.parse_args(argv)
+    {"linear": bench_linear, "attention": bench_attention, "sample": bench_sample}[a.what](a)
+    ops.check_status(ops.new_status("cuda"))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
