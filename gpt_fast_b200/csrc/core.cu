@@ -124,6 +124,51 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
     cluster.sync();                 // no block leaves while another may still read its `part`
 }
 
+// One block per row with the row held in registers: a single pass over x (float4 loads),
+// packed stores.  For D % 4 == 0 and D <= 4 * VEC_MAX * blockDim.
+constexpr int NORM_VEC_MAX = 4;
+
+template <typename TW, typename TO>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int D, float eps) {
+    __shared__ float scratch[32];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int r = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+    const int nvec = D >> 2;
+    float4 v[NORM_VEC_MAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; k++) {
+        int i = threadIdx.x + k * blockDim.x;
+        if (i < nvec) {
+            v[k] = xr[i];
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = gfb_block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; k++) {
+        int i = threadIdx.x + k * blockDim.x;
+        if (i < nvec) {
+            float o0 = v[k].x * rstd * gfb_to_f32(w[4 * i]), o1 = v[k].y * rstd * gfb_to_f32(w[4 * i + 1]);
+            float o2 = v[k].z * rstd * gfb_to_f32(w[4 * i + 2]), o3 = v[k].w * rstd * gfb_to_f32(w[4 * i + 3]);
+            TO* o = out + (size_t)r * D + 4 * i;
+            if (sizeof(TO) == 4) {
+                *reinterpret_cast<float4*>(o) = make_float4(o0, o1, o2, o3);
+            } else {
+                __nv_bfloat162 a = __floats2bfloat162_rn(o0, o1), b = __floats2bfloat162_rn(o2, o3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&a);
+                pk.y = *reinterpret_cast<uint32_t*>(&b);
+                *reinterpret_cast<uint2*>(o) = pk;
+            }
+        }
+    }
+}
+
 GFB_API int gfb_rmsnorm(float* x, const float* pending, int S, long slice, const void* w, int w_dt, void* out, int out_dt,
                         const int* rows, int R, int D, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
@@ -141,6 +186,16 @@ GFB_API int gfb_rmsnorm(float* x, const float* pending, int S, long slice, const
         return gfb_check(e, "gfb_rmsnorm (cluster)");
     }
     int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+    if (pending == nullptr && D % 4 == 0 && D <= 4 * NORM_VEC_MAX * threads) {
+#define VLAUNCH(TW, TO) e = gfb_launch(rmsnorm_vec_kernel<TW, TO>, dim3(R), dim3(threads), 0, stream, (const float*)x, (const TW*)w, (TO*)out, rows, D, eps)
+        if (w_dt == GFB_BF16 && out_dt == GFB_BF16) VLAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else if (w_dt == GFB_F32 && out_dt == GFB_BF16) VLAUNCH(float, __nv_bfloat16);
+        else if (w_dt == GFB_BF16 && out_dt == GFB_F32) VLAUNCH(__nv_bfloat16, float);
+        else if (w_dt == GFB_F32 && out_dt == GFB_F32) VLAUNCH(float, float);
+        else return gfb_fail("gfb_rmsnorm: unknown types %d %d", w_dt, out_dt);
+#undef VLAUNCH
+        return gfb_check(e, "gfb_rmsnorm (vector)");
+    }
 #define LAUNCH(TW, TO) e = gfb_launch(rmsnorm_kernel<TW, TO>, dim3(R), dim3(threads), 0, stream, x, pending, S, (size_t)slice, (const TW*)w, (TO*)out, rows, D, eps)
     if (w_dt == GFB_BF16 && out_dt == GFB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (w_dt == GFB_F32 && out_dt == GFB_BF16) LAUNCH(float, __nv_bfloat16);
@@ -261,6 +316,54 @@ __global__ void rope_append_kernel(const void* __restrict__ src_any, int S, size
     }
 }
 
+// Fast path for many tokens: bfloat16 qkv, interleaved pairs, head_dim % 8 == 0.  One thread moves
+// 8 elements (4 pairs): a 16-byte load of qkv, two 16-byte loads of (cos, sin), a 16-byte store.
+__global__ void rope_append_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                       GfbPagedKV kv, GfbBatch b, const float* __restrict__ table, int table_len,
+                                       int H, int G, int d, int append, int* status) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int t = blockIdx.x;
+    const int d8 = d >> 3;
+    const int n_items = (H + (append ? 2 * G : 0)) * d8;
+    const int item = blockIdx.y * blockDim.x + threadIdx.x;
+    if (item >= n_items) return;
+    const int s = b.tok_seq[t];
+    const int slot = b.slots[s];
+    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
+    bool ok = pos >= 0 && pos < table_len;
+    size_t cache_base = 0;
+    if (append) {
+        int pi = pos / kv.page_size, off = pos - pi * kv.page_size;
+        int page = (ok && pi < kv.max_pages) ? kv.page_table[(size_t)slot * kv.max_pages + pi] : -1;
+        if (page < 0 || page >= kv.n_pages) ok = false;
+        else cache_base = ((size_t)page * G * kv.page_size + off) * d;
+    }
+    const int head = item / d8, c = item - head * d8;          // head over q, k, v; c: which 8 elements
+    if (!ok) {
+        if (item == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+        if (head < H) *reinterpret_cast<uint4*>(q_out + ((size_t)t * H + head) * d + c * 8) = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    uint4 raw = *reinterpret_cast<const uint4*>(qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d + c * 8);
+    __nv_bfloat16* dst;
+    if (head < H) dst = q_out + ((size_t)t * H + head) * d;
+    else if (head < H + G) dst = (__nv_bfloat16*)kv.k_pool + cache_base + (size_t)(head - H) * kv.page_size * d;
+    else dst = (__nv_bfloat16*)kv.v_pool + cache_base + (size_t)(head - H - G) * kv.page_size * d;
+    if (head < H + G) {
+        const float4* cs = reinterpret_cast<const float4*>(table + ((size_t)pos * (d >> 1) + c * 4) * 2);
+        float4 cs0 = cs[0], cs1 = cs[1];                         // (cos, sin) of pairs 0,1 and 2,3
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+        float2 x0 = __bfloat1622float2(p2[0]), x1 = __bfloat1622float2(p2[1]);
+        float2 x2 = __bfloat1622float2(p2[2]), x3 = __bfloat1622float2(p2[3]);
+        p2[0] = __floats2bfloat162_rn(x0.x * cs0.x - x0.y * cs0.y, x0.y * cs0.x + x0.x * cs0.y);
+        p2[1] = __floats2bfloat162_rn(x1.x * cs0.z - x1.y * cs0.w, x1.y * cs0.z + x1.x * cs0.w);
+        p2[2] = __floats2bfloat162_rn(x2.x * cs1.x - x2.y * cs1.y, x2.y * cs1.x + x2.x * cs1.y);
+        p2[3] = __floats2bfloat162_rn(x3.x * cs1.z - x3.y * cs1.w, x3.y * cs1.z + x3.x * cs1.w);
+    }
+    *reinterpret_cast<uint4*>(dst + c * 8) = raw;
+}
+
 // src: qkv [T, (H+2G)d] of type dt, or, with n_partials > 0, float partial sums [n_partials][T][(H+2G)d].
 GFB_API int gfb_rope_append(const void* src, int n_partials, void* q_out, int dt,
                             void* k_pool, void* v_pool, const int* page_table, int max_pages, int page_size, int n_pages,
@@ -272,6 +375,13 @@ GFB_API int gfb_rope_append(const void* src, int n_partials, void* q_out, int dt
     if (d % 2) return gfb_fail("gfb_rope_append: head_dim %d is odd", d);
     GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    if (dt == GFB_BF16 && n_partials == 0 && pairing == 0 && d % 8 == 0 && n_tokens >= 64) {
+        int vitems = (H + (append ? 2 * G : 0)) * (d / 8);
+        dim3 vgrid(n_tokens, (vitems + 127) / 128);
+        cudaError_t ve = gfb_launch(rope_append_vec_kernel, vgrid, dim3(128), 0, stream, (const __nv_bfloat16*)src,
+                                    (__nv_bfloat16*)q_out, kv, b, table, table_len, H, G, d, append, status);
+        return gfb_check(ve, "gfb_rope_append (vector)");
+    }
     int items = (H + (append ? 2 * G : 0)) * (d / 2);
     dim3 grid(n_tokens, (items + 255) / 256);
     if (grid.y > 65535) return gfb_fail("gfb_rope_append: %d heads of %d exceed the grid", H + 2 * G, d);

@@ -115,3 +115,22 @@ def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal():
         torch.testing.assert_close(out[t].float(), v3, rtol=1e-2, atol=1e-2)
     for t in (200, 299):
         torch.testing.assert_close(out[t].float(), v200, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("H,G,d,q_lens,starts", [(32, 8, 128, [200, 31], [0, 77]), (6, 2, 24, [64, 70], [3, 0]), (4, 4, 16, [130], [60])])
+def test_rope_append_many_tokens(H, G, d, q_lens, starts):
+    """The 16-byte path of the rotary kernel (bfloat16, 64 tokens or more)."""
+    dtype = torch.bfloat16
+    batch, table, n_pages = make_batch(q_lens, starts, 5, 64, 8)
+    T = batch.n_tokens
+    qkv = rnd(T, (H + 2 * G) * d, dtype=dtype)
+    rt = torch.empty(8 * 64, d // 2, 2, device=DEV)
+    ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).to(DEV), rt)
+    pools = [torch.zeros(n_pages, G, 64, d, dtype=dtype, device=DEV) for _ in range(4)]
+    q, q_ref = torch.empty(T, H, d, dtype=dtype, device=DEV), torch.empty(T, H, d, dtype=dtype, device=DEV)
+    ops.rope_append(qkv, q, PagedKV(pools[0], pools[1], table, 64), batch, rt, H, G, d)
+    REF.rope_append(qkv, q_ref, PagedKV(pools[2], pools[3], table, 64), batch, rt, H, G, d)
+    ops.check_status(batch.status)
+    torch.testing.assert_close(q.float(), q_ref.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(pools[0].float(), pools[2].float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(pools[1], pools[3])
