@@ -109,8 +109,9 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
     when it draws one of `stop_tokens` (default: the model's own, may be empty).
     Requests are served batch_size at a time (default: all at once), one batch
     after another on the same cache.  callback(request_ids, tokens) is called
-    after the prefill and after every decode step with the live requests' ids
-    and their new tokens (an int32 tensor on the device)."""
+    once for the prefill and once per decode step with the ids of the requests
+    that were still running and their new tokens (an int32 tensor); a decode
+    step's call comes while the next step is already running on the GPU."""
     prompts = [list(map(int, p)) for p in prompts]
     if not prompts:
         return [], GenerationStats()
@@ -148,15 +149,36 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
             sync()
             t1 = time.perf_counter()
 
-            # live[j] = column of `history` that row j of the current decode batch fills
-            live = list(range(n))
-            n_new = [1] * n                      # tokens produced so far, per column
+            # Decode.  `live` lists the columns of `history` (sequences of this batch) still being
+            # continued.  The host looks at a step's tokens one step late: while the GPU runs step
+            # k, the host reads step k-1's tokens (copied to pinned memory behind an event) and
+            # decides who has stopped.  A sequence that drew a stop token therefore takes part in
+            # one more step, whose token is dropped; the outputs are the same as with an immediate
+            # check, and the host work no longer sits between two steps.
+            watch = bool(stops) or callback is not None
             done = [False] * n
-            cur = first
+            n_new = [1] * n                                        # tokens kept so far, per column
+
+            def look(tokens_host, cols_of_step):
+                """Digest one step's tokens: callback, stop tokens, counts."""
+                keep = [(j, t) for j, t in zip(cols_of_step, tokens_host) if not done[j]]
+                if callback is not None and keep and cols_of_step is not None:
+                    callback([req_ids[j] for j, _ in keep],
+                             torch.tensor([t for _, t in keep], dtype=torch.int32))
+                for j, t in keep:
+                    n_new[j] += 1
+                    if t in stops:
+                        done[j] = True
+
             if stops:
                 for j, t in enumerate(first.tolist()):
                     if t in stops:
                         done[j] = True
+            live = list(range(n))
+            cur = first
+            batch = None
+            pending = None                                         # (event, pinned tokens, columns) of the step in flight
+            pins = [torch.empty(n, dtype=torch.int32, pin_memory=model.device.type == "cuda") for _ in range(2)]
             row = 1
             steps = 0
             decode_tokens = 0
@@ -164,7 +186,7 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
                 keep = [j for j in live if not done[j]]
                 if not keep:
                     break
-                if keep != live or steps == 0:
+                if batch is None or keep != live:
                     idx = torch.tensor([live.index(j) for j in keep], dtype=torch.long).to(model.device)
                     nxt = cur.index_select(0, idx)
                     live = keep
@@ -174,17 +196,31 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
                     cols = torch.tensor(live, dtype=torch.long).to(model.device)
                 cur = decode_one_token(batch)
                 history[row].index_copy_(0, cols, cur)
-                if callback is not None:
-                    callback([req_ids[j] for j in live], cur)
-                for j in live:
-                    n_new[j] += 1
+                this = None
+                if watch:
+                    pin = pins[steps & 1]
+                    pin[:len(live)].copy_(cur, non_blocking=True)
+                    ev = torch.cuda.Event() if model.device.type == "cuda" else None
+                    if ev is not None:
+                        ev.record()
+                    this = (ev, pin, list(live))
+                else:
+                    for j in live:
+                        n_new[j] += 1
                 decode_tokens += len(live)
                 steps += 1
                 row += 1
-                if stops:
-                    for j, t in zip(live, cur.tolist()):
-                        if t in stops:
-                            done[j] = True
+                if pending is not None:                            # the step before this one, while this one runs
+                    ev, pin, pcols = pending
+                    if ev is not None:
+                        ev.synchronize()
+                    look(pin[:len(pcols)].tolist(), pcols)
+                pending = this
+            if pending is not None:
+                ev, pin, pcols = pending
+                if ev is not None:
+                    ev.synchronize()
+                look(pin[:len(pcols)].tolist(), pcols)
             sync()
             t2 = time.perf_counter()
             stepper.check()

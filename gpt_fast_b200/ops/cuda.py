@@ -242,7 +242,7 @@ class CudaKernels:
             splits = 1
             if batch.max_q_len == 1:       # decode: slice long sequences until about two blocks per SM work
                 pages = -(-max(batch.max_kv_len, 1) // kv.page_size)
-                splits = max(1, min(pages, 32, (2 * self.sm_count) // max(1, T * n_kv)))
+                splits = max(1, min(pages // 4, 32, (2 * self.sm_count) // max(1, T * n_kv)))
         scratch = None
         if splits > 1:
             scratch = torch.empty(T * n_head * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
