@@ -16,11 +16,19 @@ import math
 import torch
 
 
-def rms_norm(x, weight, eps):
+def rounded(x, act):
+    """Round-trip through the activation type `act` (None: leave as is).  With
+    act = bfloat16 the functions below round where the library's bfloat16 path
+    stores an activation: norm output, qkv, rotated q and k, attention output,
+    SwiGLU output; sums, softmax and the residual stream stay 32-bit."""
+    return x if act is None else x.to(act).to(x.dtype)
+
+
+def rms_norm(x, weight, eps, act=None):
     """model.py:236-241: statistics in 32-bit, cast back, then the weight."""
     x32 = x.float()
     n = x32 * torch.rsqrt(torch.mean(x32 * x32, dim=-1, keepdim=True) + eps)
-    return n.type_as(x) * weight.to(x.dtype)
+    return rounded(n.type_as(x) * weight.to(x.dtype), act)
 
 
 def rope_frequencies(head_dim, base, rope_scaling=None):
@@ -84,35 +92,36 @@ def causal_attention(q, k, v, n_head, n_kv):
     return y.transpose(0, 1).reshape(S, H * d).type_as(q)
 
 
-def attention(x, wqkv, wo, cos, sin, n_head, n_kv, head_dim):
+def attention(x, wqkv, wo, cos, sin, n_head, n_kv, head_dim, act=None):
     """model.py:191-216 without the cache: x [S, D] -> [S, D]."""
     S = x.shape[0]
     qkv = x @ wqkv.T
     q, k, v = qkv.split([n_head * head_dim, n_kv * head_dim, n_kv * head_dim], dim=-1)
-    q = apply_rope(q.view(S, n_head, head_dim), cos, sin)
-    k = apply_rope(k.view(S, n_kv, head_dim), cos, sin)
-    v = v.view(S, n_kv, head_dim)
-    y = causal_attention(q, k, v, n_head, n_kv)
+    q = rounded(apply_rope(q.view(S, n_head, head_dim), cos, sin), act)
+    k = rounded(apply_rope(k.view(S, n_kv, head_dim), cos, sin), act)
+    v = rounded(v.view(S, n_kv, head_dim), act)
+    y = rounded(causal_attention(q, k, v, n_head, n_kv), act)
     return y @ wo.T
 
 
-def feed_forward(x, w1, w2, w3):
+def feed_forward(x, w1, w2, w3, act=None):
     """model.py:226-227: w2(silu(w1 x) * w3 x)."""
-    return (torch.nn.functional.silu(x @ w1.T) * (x @ w3.T)) @ w2.T
+    return rounded(torch.nn.functional.silu(x @ w1.T) * (x @ w3.T), act) @ w2.T
 
 
-def block(x, p, prefix, cos, sin, cfg):
+def block(x, p, prefix, cos, sin, cfg, act=None):
     """model.py:161-164: h = x + attn(norm(x)); out = h + ffn(norm(h))."""
-    a = rms_norm(x, p[prefix + "attention_norm.weight"], cfg["norm_eps"])
+    a = rms_norm(x, p[prefix + "attention_norm.weight"], cfg["norm_eps"], act)
     h = x + attention(a, p[prefix + "attention.wqkv.weight"], p[prefix + "attention.wo.weight"],
-                      cos, sin, cfg["n_head"], cfg["n_local_heads"], cfg["head_dim"])
-    f = rms_norm(h, p[prefix + "ffn_norm.weight"], cfg["norm_eps"])
+                      cos, sin, cfg["n_head"], cfg["n_local_heads"], cfg["head_dim"], act)
+    f = rms_norm(h, p[prefix + "ffn_norm.weight"], cfg["norm_eps"], act)
     return h + feed_forward(f, p[prefix + "feed_forward.w1.weight"],
-                            p[prefix + "feed_forward.w2.weight"], p[prefix + "feed_forward.w3.weight"])
+                            p[prefix + "feed_forward.w2.weight"], p[prefix + "feed_forward.w3.weight"], act)
 
 
-def forward(tokens, p, cfg):
+def forward(tokens, p, cfg, act=None):
     """model.py:136-146 for one whole sequence: token ids [S] -> logits [S, V].
+    act=torch.bfloat16 rounds the activations where the library's bfloat16 path stores them.
 
     cfg keys: n_layer, n_head, n_local_heads, head_dim, norm_eps, rope_base,
     rope_scaling.  p: tensors by gpt-fast name; `output.weight` may be the
@@ -122,8 +131,8 @@ def forward(tokens, p, cfg):
     cos, sin = rope_angles(torch.arange(tokens.shape[0]), freqs)
     x = p["tok_embeddings.weight"][tokens]
     for i in range(cfg["n_layer"]):
-        x = block(x, p, f"layers.{i}.", cos, sin, cfg)
-    x = rms_norm(x, p["norm.weight"], cfg["norm_eps"])
+        x = block(x, p, f"layers.{i}.", cos, sin, cfg, act)
+    x = rms_norm(x, p["norm.weight"], cfg["norm_eps"], act)
     return x @ p["output.weight"].T
 
 

@@ -1,0 +1,79 @@
+"""The serving kernels at the layer sizes of Llama-3.1-8B (two layers, random
+weights): head_dim 128, 32 heads in 8 groups, width 4096, feed-forward 14336,
+vocabulary 128256.  The tiny configurations never reach the tensor-core
+attention kernels or the split-K / persistent products; this does."""
+import pytest
+import torch
+
+import gpt_fast_b200 as gf
+import plain_llama
+import traces
+from gpt_fast_b200.engine.replay import Replayer
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    cfg = gf.config_from_name("llama-3.1-8b")
+    cfg["num_hidden_layers"] = 2
+    cfg["max_position_embeddings"] = 4096
+    d = str(tmp_path_factory.mktemp("llama8b_2layers"))
+    gf.write_model_folder(d, cfg, seed=5)
+    p, pc = plain_llama.load_folder(d)
+    reqs = traces.make_requests(cfg["vocab_size"], [40, 3, 200, 77], seed=3)
+    ref = {"float32": {}, "bfloat16": {}}
+    for rid, toks in reqs.items():
+        for name, act in (("float32", None), ("bfloat16", torch.bfloat16)):
+            logits = plain_llama.forward(toks, p, pc, act=act)
+            for j in range(len(toks) - traces.tail_of(toks), len(toks)):
+                ref[name][(rid, j)] = logits[j]
+    return d, reqs, ref, cfg["vocab_size"]
+
+
+def run(model, steps, V):
+    rp = Replayer(model, traces.peak_tokens(steps), None)
+    out = {st["step"]: rp.run_step(st) for st in steps}
+    return traces.collect(steps, out, V)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_8b_layer_sizes_all_cuts(big, dtype):
+    folder, reqs, refs, V = big
+    ref, emu = refs["float32"], refs["bfloat16"]
+    model = gf.load(folder, dtype=dtype, device="cuda")
+    with torch.no_grad():
+        for cut, steps in (("whole", traces.whole(reqs)), ("stepped", traces.stepped(reqs)), ("batched", traces.batched(reqs, 3))):
+            rows = run(model, steps, V)
+            assert set(rows) == set(ref)
+            for key in sorted(ref):
+                got, want = torch.from_numpy(rows[key].copy()), ref[key]
+                where = f"{cut}: request {key[0]}, token {key[1]}"
+                if dtype == "float32":
+                    torch.testing.assert_close(got, want, rtol=1e-3, atol=2e-4, msg=lambda m: f"{where}\n{m}")
+                else:
+                    # How far may bfloat16 be from the 32-bit logits?  As far as the plain implementation is
+                    # when its activations are rounded to bfloat16 where the library stores them (`emu`): that
+                    # is the noise of the format on this model (about 1 % of a row's scale), measured, not
+                    # guessed.  Two ways of running the same tokens give two samples of that noise, so they are
+                    # not compared with each other but each with the 32-bit logits: the library's error must
+                    # stay within 1.5 x the plain implementation's in the mean and 2 x at the worst element.
+                    # A wrong position, head or page shows as an error of the order of the scale itself.
+                    err, noise = got - want, emu[key] - want
+                    rms = lambda t: float(t.pow(2).mean().sqrt())
+                    assert rms(err) <= 1.5 * rms(noise), f"{where}: rms error {rms(err):.4f}, bfloat16 noise {rms(noise):.4f}"
+                    assert float(err.abs().max()) <= 2.0 * float(noise.abs().max()), \
+                        f"{where}: max error {float(err.abs().max()):.4f}, bfloat16 noise {float(noise.abs().max()):.4f}"
+
+
+def test_8b_layer_sizes_greedy_tokens_agree_between_precisions(big):
+    folder, reqs, _, _ = big
+    prompts = [t[:20] for t in reqs.values() if len(t) >= 20]
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        model = gf.load(folder, dtype=dtype, device="cuda")
+        out[dtype], _ = gf.generate(model, prompts, 8, temperature=0.0, stop_tokens=[])
+    same = sum(a == b for a, b in zip(out["float32"], out["bfloat16"]))
+    first = sum(a[20] == b[20] for a, b in zip(out["float32"], out["bfloat16"]))
+    assert first == len(prompts)                     # the first new token agrees; later ones may fork on near-ties
+    assert same >= 1
