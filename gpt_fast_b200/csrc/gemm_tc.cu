@@ -134,7 +134,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -517,44 +517,50 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
-            const long total = (long)my_tiles * nkb;
-            auto coords = [&](long it, int& kb, int& row0, int& col0) {
-                const int ti = (int)(it / nkb);
-                kb = (int)(it - (long)ti * nkb);
-                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
-                row0 = (tile % row_tiles) * BM;
-                col0 = (tile / row_tiles) * PBN;
-            };
-            // prime the ring with weight tiles (no kernel writes weights), then wait for the
-            // previous kernel and add the activation tiles of the same stages
-            const long n_pre = total < (long)stages ? total : (long)stages;
-            int kb, row0, col0;
-            for (long it = 0; it < n_pre; it++) {
-                coords(it, kb, row0, col0);
-                const uint32_t full = smem_u32(&bars->full[it]);
-                mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
-                tma_load_2d(ys + (int)it * Y_TILE_BYTES, &map_y, kb * BK, col0, full);
+            // Stage, phase and tile coordinates are carried along, not recomputed: this one thread
+            // has about 500 cycles per k-block and integer divisions would eat most of them.
+            // The ring is primed with weight tiles (no kernel writes weights) before the wait for the
+            // previous kernel; the activation tiles of those stages follow it.
+            const int total = my_tiles * nkb;
+            const int n_pre = total < stages ? total : stages;
+            {
+                int kb = 0, tile = (int)blockIdx.x;
+                for (int it = 0; it < n_pre; it++) {
+                    const uint32_t full = smem_u32(&bars->full[it]);
+                    mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                    tma_load_2d(ys + it * Y_TILE_BYTES, &map_y, kb * BK, (tile / row_tiles) * PBN, full);
+                    if (++kb == nkb) { kb = 0; tile += (int)gridDim.x; }
+                }
             }
             gfb_pdl_wait();
-            for (long it = 0; it < n_pre; it++) {
-                coords(it, kb, row0, col0);
-                tma_load_2d(xs + (int)it * X_TILE_BYTES, &map_x, kb * BK, row0, smem_u32(&bars->full[it]));
-            }
-            for (long it = n_pre; it < total; it++) {
-                coords(it, kb, row0, col0);
-                const int s = (int)(it % stages);
-                const uint32_t ph = (uint32_t)(it / stages) & 1u;
-                if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+            int kb = 0, tile = (int)blockIdx.x;
+            int row0 = (tile % row_tiles) * BM, col0 = (tile / row_tiles) * PBN;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int it = 0; it < total; it++) {
                 const uint32_t full = smem_u32(&bars->full[s]);
-                mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
-                tma_load_2d(xs + s * X_TILE_BYTES, &map_x, kb * BK, row0, full);
-                tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, kb * BK, col0, full);
+                if (it < n_pre) {
+                    tma_load_2d(xs + s * X_TILE_BYTES, &map_x, kb * BK, row0, full);
+                } else {
+                    if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+                    mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+                    tma_load_2d(xs + s * X_TILE_BYTES, &map_x, kb * BK, row0, full);
+                    tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, kb * BK, col0, full);
+                }
+                if (++s == stages) { s = 0; ph ^= 1u; }
+                if (++kb == nkb) {
+                    kb = 0;
+                    tile += (int)gridDim.x;
+                    row0 = (tile % row_tiles) * BM;
+                    col0 = (tile / row_tiles) * PBN;
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BM, PBN);
-            long it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int ti = 0; ti < my_tiles && ok; ti++) {
                 const int ab = ti & 1;
@@ -562,9 +568,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem + (uint32_t)(ab * PBN);
-                for (int kb = 0; kb < nkb; kb++, it++) {
-                    const int s = (int)(it % stages);
-                    const uint32_t ph = (uint32_t)(it / stages) & 1u;
+                for (int kb = 0; kb < nkb; kb++) {
                     ok = mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag, status, 2);
                     if (!ok) break;
                     tc_fence_after();
@@ -573,6 +577,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
                     umma_commit(smem_u32(&bars->empty[s]));
+                    if (++s == stages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(smem_u32(&bars->acc_full[ab]));
             }
@@ -609,6 +614,177 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ---- pairs of SMs: cta_group::2 ---------------------------------------------------------------
+// Two blocks of a cluster work as one 256 x 256 tile: each loads its own 128 rows of the
+// activations and HALF of the weight tile (128 of the 256 weight rows); one tcgen05.mma issued by
+// the leader block multiplies with operands from both blocks' shared memory and writes 128
+// accumulator rows into each block's tensor memory.  Per SM this halves the weight-operand traffic
+// into and out of shared memory, which is what bounds the one-SM 128 x 256 tile.  No TMA
+// multicast is used: every block issues its own loads (with .cta_group::2 so that they may signal
+// the leader's barrier).  Barriers: `full` lives in the leader and counts the bytes of both
+// blocks' loads; the MMA's commit is multicast to both blocks' `empty` and `acc_full`; both
+// blocks' epilogue warps arrive on the leader's `acc_empty`.
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;      // clears the bit that tells the two blocks of a pair apart
+constexpr int PAIR_STAGE_BYTES = 2 * X_TILE_BYTES;   // 128 activation rows + 128 weight rows, 64 k each
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {      // arrives on `bar` in both blocks
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int EPI, typename TO>
+__global__ void __launch_bounds__(192)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                    TO* __restrict__ out, int R, int Cc, int K, int ldo, int stages, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t xs = base;
+    const uint32_t ys = base + (uint32_t)stages * X_TILE_BYTES;
+    float* staging = reinterpret_cast<float*>(aligned + (size_t)stages * PAIR_STAGE_BYTES);
+    PBarriers* bars = reinterpret_cast<PBarriers*>(aligned + (size_t)stages * PAIR_STAGE_BYTES + P_STAGING_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+    const int row_tiles = (R + 255) / 256, col_tiles = (Cc + 255) / 256;
+    const int n_tiles = row_tiles * col_tiles;
+    const int nkb = (K + BK - 1) / BK;
+    const int my_tiles = pair < n_tiles ? (n_tiles - 1 - pair) / n_pairs + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(smem_u32(&bars->acc_full[a]), 1);
+            mbar_init(smem_u32(&bars->acc_empty[a]), 8);       // four epilogue warps in each of the two blocks
+        }
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                          // both blocks' barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int total = my_tiles * nkb;
+            int kb = 0, tile = pair, s = 0;
+            uint32_t ph = 0;
+            int row0 = (tile % row_tiles) * 256 + (int)rank * 128, wrow0 = (tile / row_tiles) * 256 + (int)rank * 128;
+            for (int it = 0; it < total; it++) {
+                if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+                const uint32_t full = smem_u32(&bars->full[s]) & PEER_MASK;        // the leader's barrier
+                if (leader) mbar_expect_tx(smem_u32(&bars->full[s]), 2 * PAIR_STAGE_BYTES);
+                tma_load_2d_pair(xs + s * X_TILE_BYTES, &map_x, kb * BK, row0, full);
+                tma_load_2d_pair(ys + s * X_TILE_BYTES, &map_y, kb * BK, wrow0, full);
+                if (++s == stages) { s = 0; ph ^= 1u; }
+                if (++kb == nkb) {
+                    kb = 0;
+                    tile += n_pairs;
+                    row0 = (tile % row_tiles) * 256 + (int)rank * 128;
+                    wrow0 = (tile / row_tiles) * 256 + (int)rank * 128;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_idesc(256, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = 0; ti < my_tiles && ok; ti++) {
+                const int ab = ti & 1;
+                ok = mbar_wait(smem_u32(&bars->acc_empty[ab]), ((uint32_t)(ti >> 1) & 1u) ^ 1u, abort_flag, status, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)(ab * 256);
+                for (int kb = 0; kb < nkb; kb++) {
+                    ok = mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag, status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = umma_smem_desc(xs + s * X_TILE_BYTES);
+                    const uint64_t db = umma_smem_desc(ys + s * X_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) umma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit_pair(smem_u32(&bars->empty[s]));
+                    if (++s == stages) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit_pair(smem_u32(&bars->acc_full[ab]));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        float* stage = staging + q * 32 * PSP;
+        for (int ti = 0; ti < my_tiles; ti++) {
+            const int ab = ti & 1;
+            const int tile = pair + ti * n_pairs;
+            const int row0 = (tile % row_tiles) * 256 + (int)rank * 128, col0 = (tile / row_tiles) * 256;
+            if (!mbar_wait(smem_u32(&bars->acc_full[ab]), (uint32_t)(ti >> 1) & 1u, abort_flag, status, 3)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * 256);
+            const int rows = min(32, R - (row0 + q * 32));
+#pragma unroll 1
+            for (int c0 = 0; c0 < 256; c0 += PCW) {
+                if (col0 + c0 >= Cc || rows <= 0) break;
+                drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&bars->acc_empty[ab]) & PEER_MASK);
+        }
+    }
+
+    if (*abort_flag) {
+        unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 50000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                          // neither block leaves while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -716,6 +892,29 @@ int launch_persistent(const CUtensorMap& mx, const CUtensorMap& my, void* out, i
     return gfb_check(e, "gfb_gemm_tc (persistent)");
 }
 
+size_t pair_smem_bytes(int stages) {
+    return 1024 + (size_t)stages * PAIR_STAGE_BYTES + P_STAGING_BYTES + sizeof(PBarriers);
+}
+
+template <int EPI, typename TO>
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& my, void* out, int R, int Cc, int K, int ldo, int stages,
+                int sm_count, int* status, cudaStream_t stream) {
+    auto kern = gemm_tc_pair_kernel<EPI, TO>;
+    size_t smem = pair_smem_bytes(stages);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gfb_fail("gfb_gemm_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = smem;
+    }
+    int tiles = ((R + 255) / 256) * ((Cc + 255) / 256);
+    int pairs = sm_count / 2;
+    if (tiles < pairs) pairs = tiles;
+    cudaError_t e = gfb_launch_cluster(kern, dim3(2 * pairs), dim3(192), smem, stream, 2u, mx, my, (TO*)out, R, Cc, K, ldo,
+                                       stages, status);
+    return gfb_check(e, "gfb_gemm_tc (pair)");
+}
+
 template <int BN, bool SWAP>
 int dispatch_epi(int epi, int out_dt, const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, int R,
                  int Cc, int K, int ldo, int splits, int kbps, int stages, int* status, cudaStream_t stream) {
@@ -747,8 +946,8 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     if (epi == EPI_SWIGLU && N % 16) return gfb_fail("gfb_gemm_tc: SwiGLU needs N %% 16 == 0, got %d", N);
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc: operands must be 16-byte aligned");
     if (stages < 2 || stages > MAX_STAGES) return gfb_fail("gfb_gemm_tc: stages = %d out of range", stages);
-    if (bn != 512 && smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
-    if (!swap && bn != 512 && (size_t)stages * (X_TILE_BYTES + bn * BK * 2) < staging_bytes(bn))
+    if (bn < 512 && smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
+    if (!swap && bn < 512 && (size_t)stages * (X_TILE_BYTES + bn * BK * 2) < staging_bytes(bn))
         return gfb_fail("gfb_gemm_tc: %d stages are too few to stage a 128 x %d accumulator", stages, bn);
     const int total_kb = (K + BK - 1) / BK;
     if (splits < 1) splits = 1;
@@ -763,9 +962,27 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     const int R = swap ? N : M, Cc = swap ? M : N;
     CUtensorMap mx, my;
     if (make_map(&mx, swap ? W : A, R, K, BM)) return 1;
-    if (make_map(&my, swap ? A : W, Cc, K, bn == 512 ? PBN : bn)) return 1;
+    if (make_map(&my, swap ? A : W, Cc, K, bn >= 512 ? PBN : bn)) return 1;
     const int kernel_epi = splits > 1 ? EPI_PARTIAL : epi;
     int rc;
+    if (!swap && bn == 1024) {
+        // pairs of SMs: 256 x 256 tiles with cta_group::2
+        static int sm_count2 = 0;
+        if (sm_count2 == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sm_count2, cudaDevAttrMultiProcessorCount, dev);
+        }
+        int st = stages;
+        while (st > 2 && pair_smem_bytes(st) > 227 * 1024) st--;
+        CUtensorMap my2;
+        if (make_map(&my2, W, N, K, 128)) return 1;
+        typedef __nv_bfloat16 bf16;
+        if (epi == EPI_ADD) return launch_pair<EPI_ADD, float>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
+        if (epi == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
+        if (out_dt == GFB_F32) return launch_pair<EPI_STORE, float>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
+        return launch_pair<EPI_STORE, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
+    }
     if (!swap && bn == 512) {
         // persistent kernel: 128 x 256 tiles, two accumulators in tensor memory
         static int sm_count = 0;

@@ -174,7 +174,8 @@ class CudaKernels:
     def tc_plan(self, M, N, K):
         """(swap, bn, splits, stages) for the tensor-core product.  Few tokens: the weight rows fill the
         128 MMA rows and the tokens are its columns, split over K until about two blocks per SM stream
-        weights; many tokens: 128 tokens x 256 weight rows per block."""
+        weights; many tokens: 256 x 256 tiles on pairs of SMs (bn = 1024 names that kernel, 512 the
+        one-SM persistent kernel, 128/256 one tile per block)."""
         if M <= 128:
             bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
             blocks = -(-N // 128)
@@ -184,10 +185,9 @@ class CudaKernels:
             stages = max(2, min(8, (100 * 1024) // stage))
             return 1, bn, splits, stages
         if N >= 256:
-            tiles = -(-M // 128) * -(-N // 256)
-            # many tiles per SM: the persistent kernel (bn 512 = 128 x 256 tiles, two accumulators, the
-            # epilogue hidden behind the next tile); few: one tile per block
-            return 0, (512 if tiles >= 4 * self.sm_count else 256), 1, 4
+            # pairs of SMs on 256 x 256 tiles (bn 1024 = the cta_group::2 kernel), persistent, two
+            # accumulators in tensor memory so that a tile's epilogue hides behind the next main loop
+            return 0, 1024, 1, 6
         return 0, 128, 1, 6
 
     @property

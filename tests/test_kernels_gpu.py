@@ -327,7 +327,7 @@ def test_linear_tensor_core(mode, M, N, K):
 
 
 @pytest.mark.parametrize("swap,bn,splits,stages", [(1, 16, 1, 2), (1, 16, 3, 6), (1, 32, 2, 4), (1, 64, 5, 3), (1, 128, 1, 4),
-                                                   (1, 128, 4, 3), (0, 128, 1, 3), (0, 128, 1, 6), (0, 256, 1, 4), (0, 256, 1, 3), (0, 512, 1, 4), (0, 512, 1, 2)])
+                                                   (1, 128, 4, 3), (0, 128, 1, 3), (0, 128, 1, 6), (0, 256, 1, 4), (0, 256, 1, 3), (0, 512, 1, 4), (0, 512, 1, 2), (0, 1024, 1, 6), (0, 1024, 1, 3)])
 @pytest.mark.parametrize("mode", ["store", "add", "swiglu"])
 def test_tensor_core_plans(swap, bn, splits, stages, mode):
     """Every orientation, tile width, split and ring depth gives the same product."""
