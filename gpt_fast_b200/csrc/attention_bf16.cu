@@ -424,9 +424,11 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     const int rep = H / G;
     const int TQ = PREFILL_ROWS / rep;                         // query tokens per block
     // which sequence and which of its tiles is this block?
+    // Later tiles of a sequence see more keys; blocks are handed out in order of their index, so the
+    // index runs backwards over the tiles and the long ones start first.
     int seq = -1, tq0 = 0;
     {
-        int left = blockIdx.x;
+        int left = (int)gridDim.x - 1 - (int)blockIdx.x;
         for (int i = 0; i < b.n_seqs; i++) {
             int qlen = b.cu_seqlens[i + 1] - b.cu_seqlens[i];
             int nt = (qlen + TQ - 1) / TQ;
@@ -519,26 +521,35 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
                 mma_16816(sc[n + 1], qa[k], b2, b3);
             }
         }
-        // scale, mask, online softmax (row i of this thread: accumulator elements 2i, 2i+1)
+        // online softmax (row i of this thread: accumulator elements 2i, 2i+1).  Scores stay unscaled;
+        // the scale goes into the exponent: p = exp2(s * c - m * c).  Only pages that touch the
+        // diagonal, the window's edge or idle rows need the mask.
+        const bool need_mask = (p + 1) * PAGE - 1 > pos0 || window > 0 || nq * rep < PREFILL_ROWS;
+        if (need_mask) {
+#pragma unroll
+            for (int n = 0; n < 8; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int i = e >> 1;
+                    const int j = p * PAGE + n * 8 + 2 * t4 + (e & 1);
+                    if (!(row_ok[i] && j <= row_pos[i] && j >= row_lo[i])) sc[n][e] = -INFINITY;
+                }
+        }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int n = 0; n < 8; n++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int i = e >> 1;
-                const int j = p * PAGE + n * 8 + 2 * t4 + (e & 1);
-                float x = (row_ok[i] && j <= row_pos[i] && j >= row_lo[i]) ? sc[n][e] * scale_log2e : -INFINITY;
-                sc[n][e] = x;
-                mx[i] = fmaxf(mx[i], x);
-            }
-        float corr[2];
+        for (int n = 0; n < 8; n++) {
+            mx[0] = fmaxf(mx[0], fmaxf(sc[n][0], sc[n][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(sc[n][2], sc[n][3]));
+        }
+        float corr[2], mneg[2];
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-            float m_new = fmaxf(m_run[i], mx[i]);
-            corr[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f(m_run[i] - m_new);     // m_new >= m_run: finite here if m_run is
+            float m_new = fmaxf(m_run[i], mx[i]);                 // in units of the raw score
+            corr[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f((m_run[i] - m_new) * scale_log2e);
             m_run[i] = m_new;
+            mneg[i] = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;   // all masked so far: exp2(-inf) = 0 anyway
         }
         float rs[2] = {0.f, 0.f};
 #pragma unroll
@@ -546,7 +557,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int i = e >> 1;
-                float pe = (sc[n][e] == -INFINITY) ? 0.f : exp2f(sc[n][e] - m_run[i]);
+                float pe = exp2f(fmaf(sc[n][e], scale_log2e, mneg[i]));   // exp2(-inf) = 0 for masked scores
                 sc[n][e] = pe;
                 rs[i] += pe;
             }
