@@ -104,8 +104,8 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
 // token_index[index_map[b]] (index_map optional).  noise_out (optional, [B,V]) receives q.
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temp, int top_k,
-              uint64_t seed, const int64_t* __restrict__ request_ids, const int* __restrict__ token_index,
-              const int* __restrict__ index_map, float* __restrict__ noise_out) {
+              uint64_t seed, const uint64_t* __restrict__ seed_dev, const int64_t* __restrict__ request_ids,
+              const int* __restrict__ token_index, const int* __restrict__ index_map, float* __restrict__ noise_out) {
     __shared__ unsigned int hist[256];
     __shared__ float sv[32];
     __shared__ int si[32];
@@ -113,6 +113,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
     __shared__ int sh_remaining;
     gfb_pdl_launch();
     gfb_pdl_wait();
+    if (seed_dev != nullptr) seed = *seed_dev;
     const float* row = logits + (size_t)blockIdx.x * V;
 
     // pivot = k-th largest scaled logit (everything when top_k <= 0 or >= V)
@@ -183,8 +184,9 @@ constexpr int SAMPLE_REGS = 32;
 template <bool GREEDY>
 __global__ void __launch_bounds__(THREADS)
 sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temp, int top_k,
-                      uint64_t seed, const int64_t* __restrict__ request_ids, const int* __restrict__ token_index,
-                      const int* __restrict__ index_map, float* __restrict__ noise_out) {
+                      uint64_t seed, const uint64_t* __restrict__ seed_dev, const int64_t* __restrict__ request_ids,
+                      const int* __restrict__ token_index, const int* __restrict__ index_map,
+                      float* __restrict__ noise_out) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ unsigned int hist[256];
@@ -198,6 +200,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, i
     __shared__ int sh_remaining;
     gfb_pdl_launch();
     gfb_pdl_wait();
+    if (seed_dev != nullptr) seed = *seed_dev;
     const int rowi = blockIdx.y;
     const int rank = (int)cluster.block_rank();
     const float* row = logits + (size_t)rowi * V;
@@ -291,26 +294,28 @@ GFB_API int gfb_argmax(const float* logits, int* out, int B, int V, cudaStream_t
     cudaError_t e;
     if (V <= SAMPLE_CLUSTER * THREADS * SAMPLE_REGS && B <= 65535)
         e = gfb_launch_cluster(sample_cluster_kernel<true>, dim3(SAMPLE_CLUSTER, B), dim3(THREADS), 0, stream, SAMPLE_CLUSTER,
-                               logits, out, V, 1.0f, 0, (uint64_t)0, (const int64_t*)nullptr, (const int*)nullptr,
-                               (const int*)nullptr, (float*)nullptr);
+                               logits, out, V, 1.0f, 0, (uint64_t)0, (const uint64_t*)nullptr, (const int64_t*)nullptr,
+                               (const int*)nullptr, (const int*)nullptr, (float*)nullptr);
     else
         e = gfb_launch(argmax_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V);
     return gfb_check(e, "gfb_argmax");
 }
 
+// seed_dev (optional): the seed is read from device memory instead (so that a captured graph can be
+// replayed with another seed).
 GFB_API int gfb_sample(const float* logits, int* out, int B, int V, float temperature, int top_k,
-                       unsigned long long seed, const long long* request_ids, const int* token_index,
-                       const int* index_map, float* noise_out, cudaStream_t stream) {
+                       unsigned long long seed, const unsigned long long* seed_dev, const long long* request_ids,
+                       const int* token_index, const int* index_map, float* noise_out, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return gfb_fail("gfb_sample: V = %d", V);
     float t = temperature > 1e-5f ? temperature : 1e-5f;
     cudaError_t e;
     if (V <= SAMPLE_CLUSTER * THREADS * SAMPLE_REGS && B <= 65535)
         e = gfb_launch_cluster(sample_cluster_kernel<false>, dim3(SAMPLE_CLUSTER, B), dim3(THREADS), 0, stream, SAMPLE_CLUSTER,
-                               logits, out, V, t, top_k, (uint64_t)seed, (const int64_t*)request_ids, token_index, index_map,
-                               noise_out);
+                               logits, out, V, t, top_k, (uint64_t)seed, (const uint64_t*)seed_dev, (const int64_t*)request_ids,
+                               token_index, index_map, noise_out);
     else
         e = gfb_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, out, V, t, top_k, (uint64_t)seed,
-                       (const int64_t*)request_ids, token_index, index_map, noise_out);
+                       (const uint64_t*)seed_dev, (const int64_t*)request_ids, token_index, index_map, noise_out);
     return gfb_check(e, "gfb_sample");
 }

@@ -35,17 +35,26 @@ class GenerationStats:
 
 
 class _Sampler:
-    """Launches the sampling kernel for a fixed set of requests; the token
+    """Launches the sampling kernel for a fixed number of requests; the token
     index of a row is its sequence's length on the device (the position the
-    new token will take), read through the batch's slots."""
+    new token will take), read through the batch's slots.  Request ids and seed
+    live in device memory, so that a captured decode graph can serve another
+    call: `retarget` rewrites them in place."""
 
     def __init__(self, params: SamplingParams, request_ids: Sequence[int], device):
-        self.params = params
+        self.temperature, self.top_k = params.temperature, params.top_k
         self.request_ids = torch.tensor(list(request_ids), dtype=torch.int64).to(device)
+        self.seed = torch.tensor([params.seed & (2 ** 63 - 1)], dtype=torch.int64).to(device)
+
+    def key(self):
+        return (self.temperature, self.top_k, self.request_ids.shape[0])
+
+    def retarget(self, params: SamplingParams, request_ids: Sequence[int]) -> None:
+        self.request_ids.copy_(torch.tensor(list(request_ids), dtype=torch.int64), non_blocking=True)
+        self.seed.copy_(torch.tensor([params.seed & (2 ** 63 - 1)], dtype=torch.int64), non_blocking=True)
 
     def __call__(self, logits, tokens_out, batch):
-        p = self.params
-        sample(logits, p.temperature, p.top_k, seed=p.seed, request_ids=self.request_ids,
+        sample(logits, self.temperature, self.top_k, seed=0, seed_dev=self.seed, request_ids=self.request_ids,
                token_index=batch.lengths, index_map=batch.slots, out=tokens_out)
 
 
@@ -124,10 +133,12 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
     params = SamplingParams(temperature, top_k, seed)
     lens = [len(p) for p in prompts]
     if cache is None:
+        # like gpt-fast's setup_caches (model.py:117-119): the model keeps its cache and only replaces
+        # it when a call needs more
         from ..cache.paged import DEFAULT_PAGE_SIZE
-        cache = model.new_cache(cache_tokens_needed(lens, max_new_tokens, batch_size, DEFAULT_PAGE_SIZE),
-                                max_seqs=min(batch_size, len(prompts)))
-    stepper = Stepper(model, cache)
+        cache = model.default_cache(cache_tokens_needed(lens, max_new_tokens, batch_size, DEFAULT_PAGE_SIZE),
+                                    min(batch_size, len(prompts)), max(lens) + max_new_tokens)
+    stepper = Stepper.of(model, cache)
     stats = GenerationStats()
     results: List[Optional[List[int]]] = [None] * len(prompts)
     sync = torch.cuda.synchronize if model.device.type == "cuda" else (lambda: None)
@@ -190,8 +201,7 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
                     idx = torch.tensor([live.index(j) for j in keep], dtype=torch.long).to(model.device)
                     nxt = cur.index_select(0, idx)
                     live = keep
-                    batch = DecodeBatch(stepper, [slots[j] for j in live], use_graph,
-                                        _Sampler(params, [req_ids[j] for j in live], model.device))
+                    batch = stepper.decode_batch([slots[j] for j in live], use_graph, params, [req_ids[j] for j in live])
                     batch.tokens.copy_(nxt)
                     cols = torch.tensor(live, dtype=torch.long).to(model.device)
                 cur = decode_one_token(batch)

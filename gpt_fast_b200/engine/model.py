@@ -145,6 +145,19 @@ class Transformer:
             p.prepare(cache.max_pages * cache.page_size, self.device)
         return cache
 
+    def default_cache(self, max_tokens: int, max_seqs: int, max_seq_len: int) -> Cache:
+        """The cache `generate` uses when none is given: kept between calls and replaced only when a
+        call needs more tokens, sequences or length than it has (gpt-fast's setup_caches grows the
+        same way, model.py:117-119)."""
+        c = getattr(self, "_default_cache", None)
+        if (c is None or c.n_pages * c.page_size < max_tokens or c.n_slots < max_seqs or c.max_seq_len < max_seq_len
+                or c.slots.n_free != c.n_slots):
+            self._default_cache = None            # let the old pools go before the new ones are made
+            c = self.new_cache(max_tokens, max_seqs=max_seqs,
+                               max_seq_len=min(max(max_seq_len, 1), self.spec.max_position or max_seq_len))
+            self._default_cache = c
+        return c
+
     # ---- one step ------------------------------------------------------------------------
     def forward(self, tokens: torch.Tensor, batch: BatchMeta, cache: Cache,
                 want_rows: Optional[torch.Tensor], n_want: Optional[int] = None) -> torch.Tensor:

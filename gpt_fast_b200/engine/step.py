@@ -32,6 +32,17 @@ class Stepper:
         self.device = model.device
         self.status = ops.new_status(self.device)
         self._pin = self.device.type == "cuda"
+        self._decode_batches = {}
+
+    @classmethod
+    def of(cls, model: Transformer, cache: Cache) -> "Stepper":
+        """The stepper that belongs to `cache` (made on first use): it keeps the decode graphs that
+        were captured for this cache, so that later calls replay them instead of capturing again."""
+        st = getattr(cache, "_stepper", None)
+        if st is None or st.model is not model:
+            st = cls(model, cache)
+            cache._stepper = st
+        return st
 
     # ---- general step ----------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> torch.Tensor:
@@ -98,8 +109,23 @@ class Stepper:
         ops.check_status(self.status)
 
     # ---- fixed-shape decode ----------------------------------------------------------------
-    def decode_batch(self, slots: Sequence[int], use_graph: bool = True) -> "DecodeBatch":
-        return DecodeBatch(self, slots, use_graph)
+    def decode_batch(self, slots: Sequence[int], use_graph: bool = True, sampling=None, request_ids=None) -> "DecodeBatch":
+        """The fixed-shape decode step for these slots.  With `sampling` (a SamplingParams) the step
+        also draws the next tokens.  A batch made earlier for the same slots and the same sampling
+        constants is handed out again, with its captured graph; request ids and seed are rewritten."""
+        if sampling is None:
+            return DecodeBatch(self, slots, use_graph)
+        from .generate import _Sampler
+        key = (tuple(slots), bool(use_graph), sampling.temperature, sampling.top_k)
+        batch = self._decode_batches.get(key)
+        if batch is None:
+            if len(self._decode_batches) >= 64:
+                self._decode_batches.clear()
+            batch = DecodeBatch(self, slots, use_graph, _Sampler(sampling, request_ids, self.device))
+            self._decode_batches[key] = batch
+        else:
+            batch.sampler.retarget(sampling, request_ids)
+        return batch
 
 
 class DecodeBatch:

@@ -134,8 +134,9 @@ def argmax(logits, out):
 
 
 def sample(logits, out, temperature: float, top_k: Optional[int], seed: int, request_ids=None, token_index=None,
-           index_map=None, noise_out=None):
+           index_map=None, noise_out=None, seed_dev=None):
     """Temperature / top-k / exponential-race draw per row of float32 logits.
     The noise of row b is keyed by (seed, request_ids[b], token_index[index_map[b]
-    or b], vocabulary index), so it does not depend on the row's place in the batch."""
-    return kernels().sample(logits, out, temperature, top_k, seed, request_ids, token_index, index_map, noise_out)
+    or b], vocabulary index), so it does not depend on the row's place in the batch.
+    seed_dev (int64 [1] on the device) overrides `seed`: a captured graph can then be replayed with another seed."""
+    return kernels().sample(logits, out, temperature, top_k, seed, request_ids, token_index, index_map, noise_out, seed_dev)

@@ -258,7 +258,7 @@ class CudaKernels:
         self._call("sampling", "gfb_argmax", _ptr(logits), _ptr(out), c_int(B), c_int(V), _stream())
 
     def sample(self, logits, out, temperature, top_k, seed, request_ids=None, token_index=None, index_map=None,
-               noise_out=None):
+               noise_out=None, seed_dev=None):
         B, V = logits.shape
         _need(logits, torch.float32, name="logits")
         _need(out, torch.int32, (B,), "token output")
@@ -273,5 +273,5 @@ class CudaKernels:
         if noise_out is not None:
             _need(noise_out, torch.float32, (B, V), "noise output")
         self._call("sampling", "gfb_sample", _ptr(logits), _ptr(out), c_int(B), c_int(V), c_float(temperature),
-                   c_int(int(top_k) if top_k else 0), c_ulonglong(seed & (2 ** 64 - 1)), _ptr(request_ids),
+                   c_int(int(top_k) if top_k else 0), c_ulonglong(seed & (2 ** 64 - 1)), _ptr(seed_dev), _ptr(request_ids),
                    _ptr(token_index), _ptr(index_map), _ptr(noise_out), _stream())

@@ -29,7 +29,8 @@ class SamplingParams:
 
 def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] = None, *, seed: int = 0,
            request_ids: Optional[torch.Tensor] = None, token_index: Optional[torch.Tensor] = None,
-           index_map: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           index_map: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+           seed_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """logits float32 [B, V] -> token ids int32 [B].
 
     request_ids (int64 [B]) and token_index (int32; row b uses
@@ -46,5 +47,5 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] 
     if temperature == 0:
         ops.argmax(logits, out)
     else:
-        ops.sample(logits, out, temperature, top_k, seed, request_ids, token_index, index_map)
+        ops.sample(logits, out, temperature, top_k, seed, request_ids, token_index, index_map, seed_dev=seed_dev)
     return out

@@ -161,7 +161,9 @@ class PlainOps:
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
 
     def sample(self, logits, out, temperature, top_k, seed, request_ids=None, token_index=None, index_map=None,
-               noise_out=None):
+               noise_out=None, seed_dev=None):
+        if seed_dev is not None:
+            seed = int(seed_dev[0])
         B, V = logits.shape
         x = logits.float().cpu() / np.float32(max(temperature, 1e-5))
         for b in range(B):
