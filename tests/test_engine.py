@@ -46,7 +46,7 @@ def setup(request, backend, tiny_folders):
     model = gf.load(folder, dtype=dtype, device=device)
     p, cfg = plain_llama.load_folder(folder)
     reqs = traces.make_requests(cfg["vocab_size"], LENGTHS[request.param], seed=5)
-    return dict(name=request.param, model=model, p=p, cfg=cfg, reqs=reqs, dtype=dtype, device=device)
+    return dict(name=request.param, model=model, p=p, cfg=cfg, reqs=reqs, dtype=dtype, device=device, folder=folder)
 
 
 def replay(model, steps):
@@ -167,3 +167,25 @@ def test_stop_tokens_end_a_sequence_early(setup):
         cut = new.index(stop) + 1 if stop in new else len(new)
         assert q == pr + new[:cut]                              # the stop token is kept, nothing follows it
     assert len(seqs[0]) <= len(prompts[0]) + 4
+
+
+def test_repeated_calls_reuse_the_cache_and_its_decode_graphs(setup):
+    """generate() keeps the model's cache between calls, and the cache keeps the captured decode
+    steps; a later call with other prompts, another seed and other request ids must give what a
+    fresh model gives."""
+    s = setup
+    model = s["model"]
+    prompts = [t[: max(1, len(t) // 2)] for t in s["reqs"].values()][:3]
+    other = [p[: max(1, len(p) - 1)][::-1] for p in prompts]          # no longer than the first call's: the cache fits
+    first, _ = gf.generate(model, prompts, 6, temperature=0.8, top_k=40, seed=3)
+    cache = model._default_cache
+    again, _ = gf.generate(model, other, 6, temperature=0.8, top_k=40, seed=9, first_request_id=100)
+    assert model._default_cache is cache and cache.slots.n_free == cache.n_slots      # same cache, everything given back
+    fresh = gf.load(s["folder"], dtype=s["dtype"], device=s["device"])
+    want, _ = gf.generate(fresh, other, 6, temperature=0.8, top_k=40, seed=9, first_request_id=100)
+    if s["dtype"] == "float32":
+        assert again == want
+    else:
+        assert [a[:len(p) + 1] for a, p in zip(again, other)] == [w[:len(p) + 1] for w, p in zip(want, other)]
+    repeat, _ = gf.generate(model, prompts, 6, temperature=0.8, top_k=40, seed=3)
+    assert repeat == first                                                              # and the same call gives the same tokens
