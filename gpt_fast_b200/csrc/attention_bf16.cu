@@ -27,6 +27,12 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// 2^x by the special-function unit (one instruction; exact enough for probabilities that are rounded to bfloat16)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -557,7 +563,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int i = e >> 1;
-                float pe = exp2f(fmaf(sc[n][e], scale_log2e, mneg[i]));   // exp2(-inf) = 0 for masked scores
+                float pe = fast_exp2(fmaf(sc[n][e], scale_log2e, mneg[i]));   // 2^-inf = 0 for masked scores
                 sc[n][e] = pe;
                 rs[i] += pe;
             }

@@ -1,0 +1,517 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05), head_dim 128, bfloat16.
+//
+// Causal attention of a run of new tokens over the paged cache (gpt-fast: the
+// SDPA call of model.py:209-211).  A block owns one key/value head and a tile of
+// TQ = 128 / (heads per group) consecutive query tokens of one sequence; its 128
+// rows are the (token, head of the group) pairs, one per tensor-memory lane.
+// Keys and values are visited 128 at a time (two pages of 64):
+//
+//   S = Q K^T        tcgen05.mma, A = Q and B = K from shared memory (TMA, 128B swizzle),
+//                    S (32-bit) in tensor memory, two buffers
+//   softmax          4 warps, one row per thread: tcgen05.ld of S, running maximum and sum
+//                    in 32-bit registers, P rounded to bfloat16 and stored back into
+//                    tensor memory (tcgen05.st); when the maximum moves, O is rescaled in
+//                    tensor memory
+//   O += P V         tcgen05.mma with A = P from tensor memory and B = V from shared
+//                    memory as an MN-major operand (V lies [key][dim] in the cache)
+//
+// The MMA warp issues S of the next 128 keys before it waits for P of the current
+// ones, so the tensor cores work while the softmax warps do.  Warp 0 is the TMA
+// producer (Q once through a 3-D map over [token, head, dim] that lays the rows out
+// as (token, head of group); K and V pages through 2-D maps over the pools), warp 1
+// allocates tensor memory and issues the MMAs, warps 2..5 are the softmax and
+// epilogue warps.  Every wait is bounded by wall-clock time (see gemm_tc.cu).
+#include "common.cuh"
+
+#include <cuda.h>
+
+GFB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int D = 128;                    // head_dim
+constexpr int PAGE = 64;
+constexpr int ROWS = 128;                 // query rows per block
+constexpr int KEYS = 128;                 // keys per iteration (two pages)
+constexpr int HALF_BYTES = 128 * 128;     // 128 rows x 64 elements x 2 bytes: one swizzled half tile
+constexpr int TILE_BYTES = 2 * HALF_BYTES;
+constexpr int KV_STAGES = 2;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+// tensor-memory columns
+constexpr uint32_t COL_S = 0;             // two score buffers of 128 columns
+constexpr uint32_t COL_O = 256;           // output accumulator, 128 columns
+constexpr uint32_t COL_P = 384;           // two probability buffers of 64 columns (bfloat16 pairs)
+
+struct Bars {
+    unsigned long long q_full;
+    unsigned long long k_full[KV_STAGES], k_empty[KV_STAGES];
+    unsigned long long v_full[KV_STAGES], v_empty[KV_STAGES];
+    unsigned long long s_full[2], s_empty[2];
+    unsigned long long p_ready;
+    unsigned long long pv_done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int which) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 128; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            gfb_report(status, GFB_ERR_WAIT_TIMEOUT, 100 + which, (int)(blockIdx.x + gridDim.x * blockIdx.y));
+            return false;
+        }
+        __nanosleep(64);
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+// K-major operand tile with 128-byte swizzle (rows of 128 bytes, 8-row groups 1024 bytes apart)
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand tile with 128-byte swizzle: rows are K (keys), 64 MN elements (dims) per 128-byte
+// row; 8-row groups 1024 bytes apart (stride offset), the next 64 dims one half tile further (leading offset)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(HALF_BYTES >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+          "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(192, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ page_table, int max_pages, int n_pages_pool,
+                       GfbBatch b, int H, int G, float scale_log2e, int window, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t qs = base;                                            // [2 halves][128 rows][128 B]
+    const uint32_t ks = base + TILE_BYTES;                               // KV_STAGES x same, rows = keys
+    const uint32_t vs = ks + KV_STAGES * TILE_BYTES;
+    Bars* bars = reinterpret_cast<Bars*>(aligned + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rep = H / G;
+    const int TQ = ROWS / rep;
+    // which sequence and tile (long tiles first: the index runs backwards)
+    int seq = -1, tq0 = 0;
+    {
+        int left = (int)gridDim.x - 1 - (int)blockIdx.x;
+        for (int i = 0; i < b.n_seqs; i++) {
+            int qlen = b.cu_seqlens[i + 1] - b.cu_seqlens[i];
+            int nt = (qlen + TQ - 1) / TQ;
+            if (left < nt) { seq = i; tq0 = left * TQ; break; }
+            left -= nt;
+        }
+    }
+    if (seq < 0) return;                      // uniform for the block; nothing was set up yet
+    const int g = blockIdx.y;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars->q_full), 1);
+        for (int s = 0; s < KV_STAGES; s++) {
+            mbar_init(smem_u32(&bars->k_full[s]), 1);
+            mbar_init(smem_u32(&bars->k_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_full[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(smem_u32(&bars->s_full[s]), 1);
+            mbar_init(smem_u32(&bars->s_empty[s]), 4);
+        }
+        mbar_init(smem_u32(&bars->p_ready), 4);
+        mbar_init(smem_u32(&bars->pv_done), 1);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+
+    const int t_first = b.cu_seqlens[seq];
+    const int qlen = b.cu_seqlens[seq + 1] - t_first;
+    const int nq = min(TQ, qlen - tq0);
+    const int slot = b.slots[seq];
+    const int pos0 = b.lengths[slot] + tq0;
+    const int last_pos = pos0 + nq - 1;
+    const int first_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int blk0 = first_lo / KEYS, blk1 = last_pos / KEYS + 1;        // key blocks [blk0, blk1)
+    const int n_iter = blk1 - blk0;
+    const int last_page = last_pos / PAGE;
+    const int* pt = page_table + (size_t)slot * max_pages;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // Q: rows ordered (token, head of group); a 3-D box {64 dims, rep heads, TQ tokens} per half
+            mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * 128 * rep * TQ));
+            tma_load_3d(qs, &map_q, 0, g * rep, t_first + tq0, smem_u32(&bars->q_full));
+            tma_load_3d(qs + HALF_BYTES, &map_q, 64, g * rep, t_first + tq0, smem_u32(&bars->q_full));
+            for (int j = 0; j < n_iter; j++) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+                int pg[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    int pi = (blk0 + j) * 2 + h;
+                    if (pi > last_page) pi = last_page;                 // no such page: any finite data, masked later
+                    int page = pt[pi];
+                    if (page < 0 || page >= n_pages_pool) { gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi); page = 0; }
+                    pg[h] = page;
+                }
+                if (!mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+                mbar_expect_tx(smem_u32(&bars->k_full[s]), TILE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {                           // page h -> rows 64h .. 64h+63 of both halves
+                    const int row = (pg[h] * G + g) * PAGE;
+                    tma_load_2d(ks + s * TILE_BYTES + h * (PAGE * 128), &map_k, 0, row, smem_u32(&bars->k_full[s]));
+                    tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
+                }
+                if (!mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag, status, 2)) break;
+                mbar_expect_tx(smem_u32(&bars->v_full[s]), TILE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int row = (pg[h] * G + g) * PAGE;
+                    tma_load_2d(vs + s * TILE_BYTES + h * (PAGE * 128), &map_v, 0, row, smem_u32(&bars->v_full[s]));
+                    tma_load_2d(vs + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_v, 64, row, smem_u32(&bars->v_full[s]));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16(ROWS, KEYS, 0);
+            constexpr uint32_t idesc_o = idesc_bf16(ROWS, D, 1);
+            auto issue_s = [&](int j) -> bool {
+                const int s = j % KV_STAGES, sb = j & 1;
+                if (!mbar_wait(smem_u32(&bars->k_full[s]), (uint32_t)(j / KV_STAGES) & 1u, abort_flag, status, 3)) return false;
+                if (!mbar_wait(smem_u32(&bars->s_empty[sb]), ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag, status, 4)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint32_t off = (k >> 2) * HALF_BYTES;
+                    umma_ss(tmem + COL_S + sb * 128, desc_kmajor(qs + off) + 2 * (k & 3),
+                            desc_kmajor(ks + s * TILE_BYTES + off) + 2 * (k & 3), idesc_s, k != 0);
+                }
+                umma_commit(smem_u32(&bars->s_full[sb]));
+                umma_commit(smem_u32(&bars->k_empty[s]));
+                return true;
+            };
+            bool ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag, status, 5);
+            ok = ok && issue_s(0);
+            for (int j = 0; j < n_iter && ok; j++) {
+                if (j + 1 < n_iter) ok = issue_s(j + 1);
+                if (!ok) break;
+                const int s = j % KV_STAGES;
+                ok = mbar_wait(smem_u32(&bars->v_full[s]), (uint32_t)(j / KV_STAGES) & 1u, abort_flag, status, 6);
+                ok = ok && mbar_wait(smem_u32(&bars->p_ready), (uint32_t)j & 1u, abort_flag, status, 7);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++)                           // 16 keys per MMA: 8 columns of P, 2 KB of V
+                    umma_ts(tmem + COL_O, tmem + COL_P + (j & 1) * 64 + kk * 8,
+                            desc_mnmajor(vs + s * TILE_BYTES + kk * 2048), idesc_o, (j | kk) != 0);
+                umma_commit(smem_u32(&bars->pv_done));
+                umma_commit(smem_u32(&bars->v_empty[s]));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+        const int tq = r / rep;
+        const bool row_ok = tq < nq;
+        const int row_pos = pos0 + tq;
+        const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_iter && ok; j++) {
+            const int sb = j & 1;
+            const int key0 = (blk0 + j) * KEYS;
+            ok = mbar_wait(smem_u32(&bars->s_full[sb]), (uint32_t)(j >> 1) & 1u, abort_flag, status, 8);
+            if (!ok) break;
+            tc_fence_after();
+            const bool need_mask = key0 + KEYS - 1 > pos0 || key0 < first_lo || window > 0 || nq * rep < ROWS;
+            // the whole row of this block into registers: one trip to tensor memory
+            float v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(lane_base + COL_S + sb * 128 + c * 32, v[c]);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[sb]));    // this block of S is consumed (one arrival per warp)
+            if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int kj = key0 + c * 32 + i;
+                        if (!(row_ok && kj <= row_pos && kj >= row_lo)) v[c][i] = -INFINITY;
+                    }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) mx = fmaxf(mx, v[c][i]);
+            const float m_new = fmaxf(m_run, mx);
+            const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * scale_log2e);
+            const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
+            // probabilities (2^-inf = 0 for masked scores), rounded to bfloat16 into tensor memory
+            float rs = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(fmaf(v[c][i], scale_log2e, mneg));
+                    float p1 = fast_exp2(fmaf(v[c][i + 1], scale_log2e, mneg));
+                    rs += p0 + p1;
+                    pk[i >> 1] = pack2(p0, p1);
+                }
+                tmem_st16(lane_base + COL_P + sb * 64 + c * 16, pk);
+            }
+            // O of the earlier blocks follows the new maximum (after the previous P V has landed)
+            if (j > 0) {
+                ok = mbar_wait(smem_u32(&bars->pv_done), (uint32_t)(j - 1) & 1u, abort_flag, status, 9);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        float o[32];
+                        tmem_ld32(lane_base + COL_O + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] *= corr;
+                        tmem_st32(lane_base + COL_O + c * 32, o);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready));
+            l_run = l_run * corr + rs;
+            m_run = m_new;
+        }
+        if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&bars->pv_done), (uint32_t)(n_iter - 1) & 1u, abort_flag, status, 10);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const int head = g * rep + (r - tq * rep);
+            __nv_bfloat16* dst = out + ((size_t)(t_first + tq0 + tq) * H + head) * D;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                float v[32];
+                tmem_ld32(lane_base + COL_O + c * 32, v);               // warp-collective: also for idle rows
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 pk;
+                        pk.x = pack2(v[i] * inv, v[i + 1] * inv); pk.y = pack2(v[i + 2] * inv, v[i + 3] * inv);
+                        pk.z = pack2(v[i + 4] * inv, v[i + 5] * inv); pk.w = pack2(v[i + 6] * inv, v[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 50000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+}  // namespace
+
+// Causal attention for runs of new tokens on tcgen05; head_dim 128, pages of 64, at most 8 heads per group
+// with 128 % (heads per group) == 0.
+GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (page_size != PAGE || d != D) return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim %d", PAGE, D);
+    if (G <= 0 || H % G) return gfb_fail("gfb_attn_prefill_tc: %d heads over %d groups", H, G);
+    const int rep = H / G;
+    if (rep > 8 || ROWS % rep) return gfb_fail("gfb_attn_prefill_tc: %d heads per group (1, 2, 4 or 8)", rep);
+    const int TQ = ROWS / rep;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return gfb_fail("gfb_attn_prefill_tc: the driver does not export cuTensorMapEncodeTiled");
+    CUtensorMap mq, mk, mv;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)rep, (cuuint32_t)TQ};
+        cuuint32_t es[3] = {1, 1, 1};
+        CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return gfb_fail("gfb_attn_prefill_tc: tensor map of q refused (%d)", (int)r);
+    }
+    for (int i = 0; i < 2; i++) {
+        cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)n_pages * G * PAGE};
+        cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)PAGE};
+        cuuint32_t es[2] = {1, 1};
+        CUresult r = enc(i ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, i ? v_pool : k_pool, dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return gfb_fail("gfb_attn_prefill_tc: tensor map of the cache refused (%d)", (int)r);
+    }
+    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
+        configured = smem;
+    }
+    dim3 grid((n_tokens + TQ - 1) / TQ + n_seqs, G);
+    cudaError_t e = gfb_launch(attn_prefill_tc_kernel, grid, dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                               page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
+    return gfb_check(e, "gfb_attn_prefill_tc");
+}

@@ -28,8 +28,9 @@ LIBRARIES = {
     "gemm_simt": (["gemm_simt.cu"], [], []),
     "attention_generic": (["attention_generic.cu"], [], []),
     "sampling": (["sampling.cu"], [], []),
-    "gemm_tc": (["gemm_tc.cu"], [], ["cuda"]),
+    "gemm_tc": (["gemm_tc.cu"], [], []),
     "attention_bf16": (["attention_bf16.cu"], [], []),
+    "attention_tc": (["attention_tc.cu"], [], []),
 }
 HEADERS = ["common.cuh", "attn_decode_noalloc.h"]
 
