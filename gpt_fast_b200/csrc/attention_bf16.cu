@@ -234,11 +234,60 @@ __device__ __forceinline__ void mma_rows8(float* c, uint32_t a0, uint32_t a2, ui
                  : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
-template <int D>
+// What the decode kernel starts from.  SRC_Q: q [T, H, D], rotated, and the cache already holds this step's
+// keys and values.  SRC_QKV / SRC_PARTIALS: the output of the q/k/v product [T, (H + 2G) D], in bfloat16 or as
+// the 32-bit partial sums [S][T][(H + 2G) D] of a product split over K (summed here in ascending s); the kernel
+// then rotates q and k by the token's position itself (table of (cos, sin) as for `rope_append`), appends k and
+// v to the cache and attends: one launch and no round trip of q through memory (model.py:197-211 in one kernel).
+enum { SRC_Q = 0, SRC_QKV = 1, SRC_PARTIALS = 2 };
+
+struct RopeSource {
+    const void* src;          // qkv or its partial sums
+    int S;                    // number of partial sums
+    size_t slice;             // elements between partial sums
+    const float* table;       // [table_len][D / 2][2]
+    int table_len;
+    int pairing;              // 0: pairs (2i, 2i+1); 1: pairs (i, i + D/2)
+    int append;               // 0: the layer reads a cache another layer wrote
+};
+
+// x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
+// sums in ascending order.  The loads of four partial sums (8 N values) are in flight together; a pair that is
+// not wanted repeats a wanted one's addresses, so no branch sits between the loads.
+template <int SRC, int N>
+__device__ __forceinline__ void load_pairs(const RopeSource& r, const size_t* e0, const size_t* e1, float* x0, float* x1) {
+    if (SRC == SRC_PARTIALS) {
+        const float* p = (const float*)r.src;
+#pragma unroll
+        for (int i = 0; i < N; i++) { x0[i] = 0.f; x1[i] = 0.f; }
+        for (int k = 0; k < r.S; k += 4) {
+            float a[4][N], c[4][N];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float* pk = p + (size_t)min(k + u, r.S - 1) * r.slice;
+#pragma unroll
+                for (int i = 0; i < N; i++) { a[u][i] = pk[e0[i]]; c[u][i] = pk[e1[i]]; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (k + u < r.S) {
+#pragma unroll
+                    for (int i = 0; i < N; i++) { x0[i] += a[u][i]; x1[i] += c[u][i]; }
+                }
+        }
+    } else {
+        const __nv_bfloat16* p = (const __nv_bfloat16*)r.src;
+#pragma unroll
+        for (int i = 0; i < N; i++) { x0[i] = __bfloat162float(p[e0[i]]); x1[i] = __bfloat162float(p[e1[i]]); }
+    }
+}
+
+template <int D, int SRC>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
-                       GfbPagedKV kv, GfbBatch b, int H, int G, float scale_log2e, int window, int splits, int* status) {
+                       GfbPagedKV kv, GfbBatch b, int H, int G, float scale_log2e, int window, int splits, int* status,
+                       RopeSource rs) {
     constexpr int PITCH = D + 8;                 // elements per shared-memory row
     constexpr int KSTEPS = D / 16, NT = D / 8;
     constexpr int TILE = PAGE * PITCH;           // elements per tile
@@ -261,10 +310,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = lane >> 2, t4 = lane & 3;     // row (head) and column pair of the mma fragments
 
-    for (int i = tid; i < 8 * D; i += THREADS) {
-        int row = i / D, col = i - row * D;
-        qs[row * PITCH + col] = row < rep ? q[((size_t)t * H + g * rep + row) * D + col] : __float2bfloat16_rn(0.f);
-    }
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
     auto issue = [&](int page_index, int buf) {
         int page = pt[page_index];
@@ -282,8 +327,87 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
             cp_async16(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8);
         }
     };
-    if (p0 < p1) issue(p0, 0);
+    if (p0 < p1) issue(p0, 0);                                 // in flight while q is prepared
     cp_async_commit();
+    // SRC != SRC_Q: the new key and value of this token, kept in registers by the threads that made them.  The
+    // slice that owns the last page patches them into its shared-memory copy of that page: the page may have
+    // been read before the store to the cache landed.
+    constexpr int half = D / 2;
+    bool patch = false;
+    int off = 0, new_i0 = 0, new_i1 = 1;
+    __nv_bfloat16 new0 = __float2bfloat16_rn(0.f), new1 = new0;
+    if (SRC == SRC_Q) {
+        for (int i = tid; i < 8 * D; i += THREADS) {
+            int row = i / D, col = i - row * D;
+            qs[row * PITCH + col] = row < rep ? q[((size_t)t * H + g * rep + row) * D + col] : __float2bfloat16_rn(0.f);
+        }
+    } else {
+        constexpr int IT = 8 * half / THREADS;                    // q pairs per thread; one more pair for k or v
+        const size_t W = (size_t)(H + 2 * G) * D;
+        const bool ok = pos >= 0 && pos < rs.table_len;
+        if (!ok && tid == 0 && g == 0 && z == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+        const float* cs_row = rs.table + (size_t)(ok ? pos : 0) * half * 2;
+        const int n_all = last_page - first_page + 1;
+        const int z_last = (n_all - 1) / per;
+        int page = -1;
+        if (rs.append && ok && z == z_last) {
+            off = pos - last_page * PAGE;
+            page = last_page < kv.max_pages ? pt[last_page] : -1;
+            if (page < 0 || page >= kv.n_pages) {
+                if (tid == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+                page = -1;
+            }
+        }
+        patch = page >= 0 && tid < 2 * half;
+        size_t e0[IT + 1], e1[IT + 1];
+        int qi0[IT], qi1[IT], qrow[IT], qi[IT];
+#pragma unroll
+        for (int it = 0; it < IT; it++) {
+            const int idx = tid + it * THREADS;
+            qrow[it] = idx / half;
+            qi[it] = idx - qrow[it] * half;
+            qi0[it] = rs.pairing == 1 ? qi[it] : 2 * qi[it];
+            qi1[it] = rs.pairing == 1 ? qi[it] + half : 2 * qi[it] + 1;
+            const size_t e = (size_t)t * W + (size_t)(g * rep + (qrow[it] < rep ? qrow[it] : 0)) * D;
+            e0[it] = e + qi0[it];
+            e1[it] = e + qi1[it];
+        }
+        const bool is_key = tid < half;
+        const int ki = is_key ? tid : tid - half;
+        if (patch) {
+            new_i0 = (is_key && rs.pairing == 1) ? ki : 2 * ki;
+            new_i1 = (is_key && rs.pairing == 1) ? ki + half : 2 * ki + 1;
+            const size_t e = (size_t)t * W + (size_t)(is_key ? H + g : H + G + g) * D;
+            e0[IT] = e + new_i0;
+            e1[IT] = e + new_i1;
+        } else {
+            e0[IT] = e0[0];
+            e1[IT] = e1[0];
+        }
+        float x0[IT + 1], x1[IT + 1];
+        load_pairs<SRC, IT + 1>(rs, e0, e1, x0, x1);
+#pragma unroll
+        for (int it = 0; it < IT; it++) {
+            const float2 cs = *reinterpret_cast<const float2*>(cs_row + 2 * qi[it]);
+            const bool live = ok && qrow[it] < rep;
+            qs[qrow[it] * PITCH + qi0[it]] = __float2bfloat16_rn(live ? x0[it] * cs.x - x1[it] * cs.y : 0.f);
+            qs[qrow[it] * PITCH + qi1[it]] = __float2bfloat16_rn(live ? x1[it] * cs.x + x0[it] * cs.y : 0.f);
+        }
+        if (patch) {
+            const size_t dst = (((size_t)page * G + g) * PAGE + off) * D;
+            if (is_key) {                                     // the key: rotated
+                const float2 cs = *reinterpret_cast<const float2*>(cs_row + 2 * ki);
+                new0 = __float2bfloat16_rn(x0[IT] * cs.x - x1[IT] * cs.y);
+                new1 = __float2bfloat16_rn(x1[IT] * cs.x + x0[IT] * cs.y);
+            } else {                                          // the value: copied
+                new0 = __float2bfloat16_rn(x0[IT]);
+                new1 = __float2bfloat16_rn(x1[IT]);
+            }
+            __nv_bfloat16* dp = (__nv_bfloat16*)(is_key ? kv.k_pool : kv.v_pool) + dst;
+            dp[new_i0] = new0;
+            dp[new_i1] = new1;
+        }
+    }
     __syncthreads();                                           // qs complete
 
     uint32_t qa[KSTEPS][2];
@@ -304,6 +428,14 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
+        if (SRC != SRC_Q && p == last_page) {                  // uniform: the block's last page holds the new token
+            if (patch) {
+                __nv_bfloat16* row = tiles + (2 * buf + (tid < half ? 0 : 1)) * TILE + off * PITCH;
+                row[new_i0] = new0;
+                row[new_i1] = new1;
+            }
+            __syncthreads();
+        }
         const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf) * TILE);
         const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf + 1) * TILE);
 
@@ -625,6 +757,33 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const f
     }
 }
 
+// Launch of the tensor-core decode kernel for head_dim 64 or 128 and one of the three sources: 4 padded tiles
+// + the query rows of shared memory; the merge area reuses the tiles.
+cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, const void* q, void* out, float* so, float* sml,
+                              GfbPagedKV kv, GfbBatch b, int H, int G, float scale, int window, int splits, int* status,
+                              RopeSource rs) {
+    typedef void (*Kern)(const __nv_bfloat16*, __nv_bfloat16*, float*, float*, GfbPagedKV, GfbBatch, int, int, float, int, int,
+                         int*, RopeSource);
+    static const Kern kerns[2][3] = {
+        {attn_decode_mma_kernel<64, SRC_Q>, attn_decode_mma_kernel<64, SRC_QKV>, attn_decode_mma_kernel<64, SRC_PARTIALS>},
+        {attn_decode_mma_kernel<128, SRC_Q>, attn_decode_mma_kernel<128, SRC_QKV>, attn_decode_mma_kernel<128, SRC_PARTIALS>}};
+    static bool configured[2][3] = {{false, false, false}, {false, false, false}};
+    const int di = d == 128 ? 1 : 0;
+    const size_t msmem = (size_t)(4 * PAGE + 8) * (d + 8) * 2;
+    Kern kern = kerns[di][src];
+    if (msmem > 48 * 1024 && !configured[di][src]) {
+        cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem);
+        if (a != cudaSuccess) {
+            gfb_fail("decode attention: %zu bytes of shared memory refused: %s", msmem, cudaGetErrorString(a));
+            return cudaErrorInvalidValue;
+        }
+        configured[di][src] = true;
+    }
+    gfb_error_text[0] = 0;
+    return gfb_launch(kern, grid, dim3(THREADS), msmem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b,
+                      H, G, scale * 1.4426950408889634f, window, splits, status, rs);
+}
+
 }  // namespace
 
 // Bytes of scratch the decode kernel needs for `splits` > 1: [T, H, splits, d + 2] floats.
@@ -657,17 +816,8 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     dim3 grid(n_tokens, G, splits);
     cudaError_t e;
     if (d == 128 || d == 64) {
-        // tensor-core kernel: 4 padded tiles + the query rows; the merge area reuses the tiles
-        size_t msmem = (size_t)(4 * PAGE + 8) * (d + 8) * 2;
-        static size_t mconf[2] = {0, 0};
-        auto kern = d == 128 ? attn_decode_mma_kernel<128> : attn_decode_mma_kernel<64>;
-        if (msmem > 48 * 1024 && msmem > mconf[d == 128]) {
-            cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem);
-            if (a != cudaSuccess) return gfb_fail("gfb_attn_decode: %zu bytes of shared memory refused: %s", msmem, cudaGetErrorString(a));
-            mconf[d == 128] = msmem;
-        }
-        e = gfb_launch(kern, grid, dim3(THREADS), msmem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b,
-                       H, G, scale * 1.4426950408889634f, window, splits, status);
+        e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, RopeSource{});
+        if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
     } else {
         e = gfb_launch(attn_decode_kernel, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
                        (__nv_bfloat16*)out, so, sml, kv, b, H, G, d, scale * 1.4426950408889634f, window, splits, status);
@@ -678,6 +828,38 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
         e = gfb_launch(attn_combine_kernel, cgrid, dim3(128), 0, stream, (const float*)so, (const float*)sml,
                        (__nv_bfloat16*)out, H, d, splits);
         return gfb_check(e, "gfb_attn_decode (combine)");
+    }
+    return 0;
+}
+
+// Rotary encoding, cache append and decode attention in one launch (head_dim 64 or 128, bfloat16): `src` is the
+// q/k/v product [T, (H + 2G) d] in bfloat16 (n_part = 0) or its n_part 32-bit partial sums [n_part][T][(H + 2G) d].
+// With append = 0 only q is taken from it (the layer reads a cache that another layer wrote).
+GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k_pool, void* v_pool, const int* page_table,
+                                 int max_pages, int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq,
+                                 const int* slots, const int* lengths, int n_seqs, int n_tokens, const float* table,
+                                 int table_len, int H, int G, int d, int pairing, int append, float scale, int window,
+                                 int splits, float* scratch, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (page_size != PAGE) return gfb_fail("gfb_attn_decode_rope: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
+    if (d != 64 && d != 128) return gfb_fail("gfb_attn_decode_rope: head_dim %d (64 or 128)", d);
+    if (G <= 0 || H % G || H / G > MAX_REP) return gfb_fail("gfb_attn_decode_rope: %d heads over %d groups (at most %d per group)", H, G, MAX_REP);
+    if (splits < 1 || G > 65535 || splits > 65535) return gfb_fail("gfb_attn_decode_rope: bad split count %d", splits);
+    if (splits > 1 && scratch == nullptr) return gfb_fail("gfb_attn_decode_rope: %d slices need scratch memory", splits);
+    if (pairing != 0 && pairing != 1) return gfb_fail("gfb_attn_decode_rope: unknown pairing %d", pairing);
+    GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
+    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    float* so = scratch;
+    float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
+    RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append};
+    cudaError_t e = launch_decode_mma(d, n_part > 0 ? SRC_PARTIALS : SRC_QKV, dim3(n_tokens, G, splits), stream, nullptr, out, so, sml,
+                                      kv, b, H, G, scale, window, splits, status, rs);
+    if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
+    if (gfb_check(e, "gfb_attn_decode_rope")) return 1;
+    if (splits > 1) {
+        e = gfb_launch(attn_combine_kernel, dim3(n_tokens, H), dim3(128), 0, stream, (const float*)so, (const float*)sml,
+                       (__nv_bfloat16*)out, H, d, splits);
+        return gfb_check(e, "gfb_attn_decode_rope (combine)");
     }
     return 0;
 }

@@ -118,6 +118,20 @@ def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, hea
     return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
 
 
+def rope_append_attention(qkv, partials, kv: PagedKV, batch: BatchMeta, table, out, n_head: int, n_kv: int, head_dim: int,
+                          pairing: str, append: bool, scale: float, window: Optional[int] = None):
+    """`rope_append` followed by `attention`: qkv [T, (H+2G)d] (or its deferred partial sums) -> out [T, H*d].
+    Where a kernel does both in one launch (a decode step in bfloat16) that kernel runs; q then never goes
+    through memory."""
+    k = kernels()
+    fused = getattr(k, "rope_append_attention", None)
+    if fused is not None and fused(qkv, partials, kv, batch, table, out, n_head, n_kv, head_dim, pairing, append, scale, window):
+        return
+    q = torch.empty(batch.n_tokens, n_head, head_dim, dtype=out.dtype, device=out.device)
+    k.rope_append(qkv, q, kv, batch, table, n_head, n_kv, head_dim, pairing, append, partials)
+    k.attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
+
+
 def advance_lengths(batch: BatchMeta):
     """lengths[slot] += number of new tokens, for every sequence of the batch."""
     return kernels().advance_lengths(batch)

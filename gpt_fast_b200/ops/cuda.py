@@ -256,6 +256,38 @@ class CudaKernels:
                    c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(splits),
                    _ptr(scratch), _ptr(batch.status), _stream())
 
+    def rope_append_attention(self, qkv, partials, kv, batch, table, out, n_head, n_kv, head_dim, pairing, append,
+                              scale, window=None) -> bool:
+        """Rotary encoding, cache append and attention of a decode step in one launch, where the kernel for
+        it fits (bfloat16, one token per sequence, head_dim 64 or 128, pages of 64, at most 8 query heads per
+        key/value head).  Returns False, having done nothing, where it does not."""
+        T = batch.n_tokens
+        if not (out.dtype == torch.bfloat16 and batch.max_q_len == 1 and head_dim in (64, 128) and kv.page_size == 64
+                and n_head // n_kv <= 8):
+            return False
+        W = (n_head + 2 * n_kv) * head_dim
+        if partials is not None:
+            _need(partials, torch.float32, (partials.shape[0], T, W), "partial sums of qkv")
+            src, n_part = partials, partials.shape[0]
+        else:
+            _need(qkv, torch.bfloat16, (T, W), "qkv")
+            src, n_part = qkv, 0
+        _need(out, torch.bfloat16, (T, n_head * head_dim), "attention output")
+        _need(table, torch.float32, name="rotary table")
+        _need(kv.k_pool, torch.bfloat16, name="key pool")
+        if tuple(kv.k_pool.shape[1:]) != (n_kv, kv.page_size, head_dim):
+            _fail(f"key pool pages are {tuple(kv.k_pool.shape[1:])}, the layer needs {(n_kv, kv.page_size, head_dim)}")
+        pages = -(-max(batch.max_kv_len, 1) // kv.page_size)
+        splits = max(1, min(pages // 4, 32, (2 * self.sm_count) // max(1, T * n_kv)))
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(T * n_head * splits * (head_dim + 2), dtype=torch.float32, device=out.device)
+        self._call("attention_bf16", "gfb_attn_decode_rope", _ptr(src), c_int(n_part), _ptr(out), *self._kv_args(kv),
+                   *self._batch_args(batch), _ptr(table), c_int(table.shape[0]), c_int(n_head), c_int(n_kv), c_int(head_dim),
+                   c_int(_PAIRING[pairing]), c_int(1 if append else 0), c_float(scale), c_int(window or 0), c_int(splits),
+                   _ptr(scratch), _ptr(batch.status), _stream())
+        return True
+
     # -- sampling --------------------------------------------------------------------------
     def argmax(self, logits, out):
         B, V = logits.shape

@@ -1,9 +1,9 @@
 """Causal grouped-query attention with a fused q/k/v projection
 (gpt-fast model.py:167-216).
 
-Steps: qkv = h Wqkv^T; rotate q and k by each token's position and append k, v
-to the sequence's place in the cache (one kernel); attention of the new
-queries over the cache; residual += y Wo^T.  Query head h reads key/value
+Steps: qkv = h Wqkv^T; rotate q and k by each token's position, append k, v
+to the sequence's place in the cache and attend over the cache (two kernels
+for a prompt, one for a decode step); residual += y Wo^T.  Query head h reads key/value
 head h // (n_head / n_kv); the scale is 1/sqrt(head_dim) unless given."""
 import math
 from typing import Optional
@@ -48,8 +48,7 @@ class Attention:
         H, G, d = self.n_head, self.n_kv, self.head_dim
         qkv = torch.empty(T, (H + 2 * G) * d, dtype=self.dtype, device=h.device)
         partials = ops.linear(h, self.wqkv, qkv, defer=True)      # a split sum is finished by the rotary kernel
-        q = torch.empty(T, H, d, dtype=self.dtype, device=h.device)
-        ops.rope_append(qkv, q, view.kv, batch, self.position.table, H, G, d, self.position.pairing, append, partials)
         y = torch.empty(T, H * d, dtype=self.dtype, device=h.device)
-        ops.attention(q, view.kv, batch, y, H, G, d, self.scale, self.window)
+        ops.rope_append_attention(qkv, partials, view.kv, batch, self.position.table, y, H, G, d, self.position.pairing,
+                                  append, self.scale, self.window)
         as_residual(residual).add_linear(y, self.wo)

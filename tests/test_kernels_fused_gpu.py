@@ -134,3 +134,80 @@ def test_rope_append_many_tokens(H, G, d, q_lens, starts):
     torch.testing.assert_close(q.float(), q_ref.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(pools[0].float(), pools[2].float(), rtol=2e-2, atol=2e-2)
     assert torch.equal(pools[1], pools[3])
+
+
+DECODE_ROPE_CASES = [  # H, G, d, starts (one new token per sequence)
+    (32, 8, 128, [0, 63, 64, 130, 700, 5, 127, 1]),
+    (6, 2, 64, [0, 200, 64]),
+    (5, 5, 128, [1000]),                              # long enough to be cut into slices of the cache
+    (16, 2, 64, [33, 639]),
+]
+
+
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("pairing", ["interleaved", "half"])
+@pytest.mark.parametrize("source", ["partials", "qkv"])
+@pytest.mark.parametrize("H,G,d,starts", DECODE_ROPE_CASES)
+def test_rotary_append_and_decode_attention_in_one_kernel(window, pairing, source, H, G, d, starts):
+    """The decode step's fused kernel against the plain rotary/append followed by the plain attention: the same
+    output, and the same keys and values in the cache, at page edges, at position 0 and with a sliced cache."""
+    q_lens = [1] * len(starts)
+    batch, table, n_pages = make_batch(q_lens, starts, 9, 64, 32, seed=3)
+    T, W = batch.n_tokens, (H + 2 * G) * d
+    dt = torch.bfloat16
+    rt = torch.empty(32 * 64, d // 2, 2, device=DEV)
+    ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).to(DEV), rt)
+    k0, v0 = rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5)
+    kv, kv_ref = PagedKV(k0.clone(), v0.clone(), table, 64), PagedKV(k0.clone(), v0.clone(), table, 64)
+    if source == "partials":
+        partials, qkv = rnd(3, T, W, seed=1), torch.empty(T, W, dtype=dt, device=DEV)
+    else:
+        partials, qkv = None, rnd(T, W, dtype=dt, seed=1)
+    scale = 1 / math.sqrt(d)
+    out, ref = torch.empty(T, H * d, dtype=dt, device=DEV), torch.empty(T, H * d, dtype=dt, device=DEV)
+    assert ops.kernels().rope_append_attention(qkv, partials, kv, batch, rt, out, H, G, d, pairing, True, scale, window)
+    q_ref = torch.empty(T, H, d, dtype=dt, device=DEV)
+    REF.rope_append(qkv, q_ref, kv_ref, batch, rt, H, G, d, pairing, True, partials)
+    REF.attention(q_ref, kv_ref, batch, ref, H, G, d, scale, window)
+    ops.check_status(batch.status)
+    torch.testing.assert_close(kv.k_pool.float(), kv_ref.k_pool.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(kv.v_pool.float(), kv_ref.v_pool.float(), rtol=2e-2, atol=2e-2)
+    assert not torch.equal(kv.k_pool, k0)                                   # something was appended
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
+    # append=False: the cache (as the reference left it) is only read
+    kept = kv_ref.k_pool.clone()
+    out2 = torch.empty_like(out)
+    assert ops.kernels().rope_append_attention(qkv, partials, kv_ref, batch, rt, out2, H, G, d, pairing, False, scale, window)
+    ops.check_status(batch.status)
+    assert torch.equal(kv_ref.k_pool, kept)
+    torch.testing.assert_close(out2.float(), ref.float(), rtol=2e-2, atol=1e-2)
+
+
+def test_fused_decode_attention_sees_the_new_token_and_a_far_key():
+    """Weights cannot hide a wrong row here: the new token's own key is made to dominate for one sequence (its
+    value must come out), a key hundreds of positions back for another."""
+    H, G, d = 8, 2, 128
+    starts = [300, 300]
+    batch, table, n_pages = make_batch([1, 1], starts, 4, 64, 8, seed=1)
+    dt = torch.bfloat16
+    rt = torch.empty(8 * 64, d // 2, 2, device=DEV)
+    ops.rope_table(torch.zeros(d // 2, device=DEV), rt)                      # no rotation: keys stay what they are
+    k_pool = 0.01 * rnd(n_pages, G, 64, d, dtype=dt, seed=4)
+    v_pool = rnd(n_pages, G, 64, d, dtype=dt, seed=5)
+    W = (H + 2 * G) * d
+    qkv = 0.01 * rnd(2, W, dtype=dt, seed=6)
+    probe = torch.zeros(d, device=DEV)
+    probe[3] = 30.0
+    qkv[:, : H * d] = probe.repeat(H).to(dt)                                # every query looks along dimension 3
+    qkv[0, H * d: (H + G) * d] = probe.repeat(G).to(dt)                     # sequence 0: its own new key answers
+    slots = batch.slots.tolist()
+    far_page = int(table[slots[1], 1])                                       # sequence 1: position 64 + 9 answers
+    k_pool[far_page, :, 9, :] = probe.to(dt)
+    kv = PagedKV(k_pool, v_pool, table, 64)
+    out = torch.empty(2, H * d, dtype=dt, device=DEV)
+    assert ops.kernels().rope_append_attention(qkv, None, kv, batch, rt, out, H, G, d, "interleaved", True, 1.0, None)
+    ops.check_status(batch.status)
+    new_v = qkv[0, (H + G) * d:].view(G, d).float()
+    for h in range(H):
+        torch.testing.assert_close(out[0, h * d:(h + 1) * d].float(), new_v[h // (H // G)], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(out[1, h * d:(h + 1) * d].float(), v_pool[far_page, h // (H // G), 9].float(), rtol=2e-2, atol=2e-2)
