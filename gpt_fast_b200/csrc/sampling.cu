@@ -266,7 +266,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, i
 #pragma unroll
         for (int e = 0; e < SAMPLE_REGS; e++) {
             int i = (e * SAMPLE_CLUSTER + rank) * THREADS + threadIdx.x;
-            if (i < V) {
+            if (i < V && (x[e] >= pivot || noise_out != nullptr)) {      // noise only where it can matter: the survivors
                 float qn = race_noise(seed, request, tix, i);
                 if (noise_out) noise_out[(size_t)rowi * V + i] = qn;
                 if (x[e] >= pivot) argmax_combine(best, best_i, x[e] - logf(qn), i);

@@ -78,8 +78,21 @@ def bench_attention(a):
     meta, kv = paged_batch(a.batch, a.context, a.new, G, d)
     q = torch.randn(meta.n_tokens, H, d, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(meta.n_tokens, H * d, device="cuda", dtype=torch.bfloat16)
-    us = graph_time_us(lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d)), a.reps)
     kv_bytes = a.batch * (a.context + a.new) * G * d * 2 * 2
+    if a.new == 1 and a.partials >= 0:
+        # the decode step's kernel: rotary encoding and cache append from the q/k/v product (its partial sums), then attention
+        W = (H + 2 * G) * d
+        parts = torch.randn(a.partials, meta.n_tokens, W, device="cuda") if a.partials else None
+        qkv = torch.randn(meta.n_tokens, W, device="cuda", dtype=torch.bfloat16)
+        table = torch.empty(a.context + a.new + 64, d // 2, 2, device="cuda")
+        ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).cuda(), table)
+        us = graph_time_us(lambda i: ops.rope_append_attention(qkv, parts, kv, meta, table, out, H, G, d, "interleaved", True,
+                                                               1 / math.sqrt(d)), a.reps)
+        print(f"rotary + append + attention decode batch={a.batch} context={a.context} partial sums={a.partials}: {us:.1f} us, "
+              f"K/V at {kv_bytes / us / 1e3:.0f} GB/s")
+        ops.check_status(meta.status)
+        return
+    us = graph_time_us(lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d)), a.reps)
     if a.new == 1:
         print(f"attention decode batch={a.batch} context={a.context}: {us:.1f} us, K/V at {kv_bytes / us / 1e3:.0f} GB/s")
     else:
@@ -109,6 +122,8 @@ def main(argv=None):
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=4000)
     p.add_argument("--new", type=int, default=1); p.add_argument("--heads", type=int, default=32)
     p.add_argument("--kv_heads", type=int, default=8); p.add_argument("--head_dim", type=int, default=128)
+    p.add_argument("--partials", type=int, default=-1,
+                   help="decode only: time the fused rotary + append + attention kernel fed by this many partial sums (0: bfloat16 qkv)")
     p.add_argument("--reps", type=int, default=10)
     p = sub.add_parser("sample")
     p.add_argument("--batch", type=int, default=8); p.add_argument("--vocab", type=int, default=128256)
