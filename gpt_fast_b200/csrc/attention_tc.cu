@@ -10,8 +10,8 @@
 //                    S (32-bit) in tensor memory, two buffers
 //   softmax          4 warps, one row per thread: tcgen05.ld of S, running maximum and sum
 //                    in 32-bit registers, P rounded to bfloat16 and stored back into
-//                    tensor memory (tcgen05.st); when the maximum moves, O is rescaled in
-//                    tensor memory
+//                    tensor memory (tcgen05.st); the reference maximum follows the true one
+//                    lazily (steps of 2^8), and only then O is rescaled in tensor memory
 //   O += P V         tcgen05.mma with A = P from tensor memory and B = V from shared
 //                    memory as an MN-major operand (V lies [key][dim] in the cache)
 //
@@ -370,16 +370,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         if (!(row_ok && kj <= row_pos && kj >= row_lo)) v[c][i] = -INFINITY;
                     }
             }
-            float mx = -INFINITY;
+            float mx4[4];                                                // four chains instead of one of 128
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+            for (int c = 0; c < 4; c++) {
+                mx4[c] = v[c][0];
 #pragma unroll
-                for (int i = 0; i < 32; i++) mx = fmaxf(mx, v[c][i]);
-            const float m_new = fmaxf(m_run, mx);
-            const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * scale_log2e);
+                for (int i = 1; i < 32; i++) mx4[c] = fmaxf(mx4[c], v[c][i]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // The running maximum only has to keep the exponentials in range, so it follows the true maximum
+            // lazily: it moves (and O is rescaled) only when the true maximum has grown by more than 2^8 in
+            // the exponent; until then probabilities may reach 256, which bfloat16 and the 32-bit sums hold.
+            // Sum and output use the same reference, so the quotient at the end is exact either way.
+            float m_new = m_run;
+            if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * scale_log2e > 8.f)) m_new = mx;
+            const float corr = (m_run == -INFINITY) ? 0.f : (m_new == m_run ? 1.f : fast_exp2((m_run - m_new) * scale_log2e));
             const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
             // probabilities (2^-inf = 0 for masked scores), rounded to bfloat16 into tensor memory
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 uint32_t pk[16];
@@ -387,11 +395,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = 0; i < 32; i += 2) {
                     float p0 = fast_exp2(fmaf(v[c][i], scale_log2e, mneg));
                     float p1 = fast_exp2(fmaf(v[c][i + 1], scale_log2e, mneg));
-                    rs += p0 + p1;
+                    rs4[c] += p0 + p1;
                     pk[i >> 1] = pack2(p0, p1);
                 }
                 tmem_st16(lane_base + COL_P + sb * 64 + c * 16, pk);
             }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             // O of the earlier blocks follows the new maximum (after the previous P V has landed)
             if (j > 0) {
                 ok = mbar_wait(smem_u32(&bars->pv_done), (uint32_t)(j - 1) & 1u, abort_flag, status, 9);
