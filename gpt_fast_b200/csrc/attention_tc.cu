@@ -159,6 +159,38 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
+// The same load without the wait, and the wait as a separate step that names the registers, so that the compiler
+// keeps every use of them behind it: several loads can then be in flight before one wait.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
+// a whole row of 128 scores: four loads in flight, then the wait
+__device__ __forceinline__ void tmem_ld_row128(uint32_t taddr, float (*v)[32]) {
+    uint32_t r[4][32];
+#pragma unroll
+    for (int c = 0; c < 4; c++) tmem_ld32_issue(taddr + c * 32, r[c]);
+#pragma unroll
+    for (int c = 0; c < 4; c++) tmem_ld_wait32(r[c]);
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[c][i] = __uint_as_float(r[c][i]);
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -356,8 +388,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool need_mask = key0 + KEYS - 1 > pos0 || key0 < first_lo || window > 0 || nq * rep < ROWS;
             // the whole row of this block into registers: one trip to tensor memory
             float v[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld32(lane_base + COL_S + sb * 128 + c * 32, v[c]);
+            tmem_ld_row128(lane_base + COL_S + sb * 128, v);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[sb]));    // this block of S is consumed (one arrival per warp)
@@ -459,6 +490,321 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// ---- two query tiles per block ------------------------------------------------------------------
+// The same algorithm with TWO tiles of 128 rows (2 TQ consecutive tokens) in one block, each with its own
+// four softmax warps, sharing every K/V page that is loaded.  The tensor pipe alternates between the
+// tiles: while the warps of one tile work through their exponentials, it computes P V of the other tile
+// and that tile's next scores.  Tensor memory: S of tile x in columns 128 x .. 128 x + 127, O of tile x in
+// 256 + 128 x ...; P (bfloat16) overwrites the first 64 columns of its own S once the scores are in
+// registers, and the next S of that tile is issued behind the P V that reads it (the pipe runs in order).
+struct Bars2 {
+    unsigned long long q_full;
+    unsigned long long k_full[KV_STAGES], k_empty[KV_STAGES];
+    unsigned long long v_full[KV_STAGES], v_empty[KV_STAGES];
+    unsigned long long s_full[2];
+    unsigned long long p_ready[2];
+    unsigned long long pv_done[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(320, 1)
+attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ page_table, int max_pages, int n_pages_pool,
+                        GfbBatch b, int H, int G, float scale_log2e, int window, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t qs = base;                                            // 2 tiles x [2 halves][128 rows][128 B]
+    const uint32_t ks = base + 2 * TILE_BYTES;
+    const uint32_t vs = ks + KV_STAGES * TILE_BYTES;
+    Bars2* bars = reinterpret_cast<Bars2*>(aligned + (size_t)(2 + 2 * KV_STAGES) * TILE_BYTES);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rep = H / G;
+    const int TQ = ROWS / rep;
+    int seq = -1, tq0 = 0;
+    {
+        int left = (int)gridDim.x - 1 - (int)blockIdx.x;                 // long tiles first
+        for (int i = 0; i < b.n_seqs; i++) {
+            int qlen = b.cu_seqlens[i + 1] - b.cu_seqlens[i];
+            int nt = (qlen + 2 * TQ - 1) / (2 * TQ);
+            if (left < nt) { seq = i; tq0 = left * 2 * TQ; break; }
+            left -= nt;
+        }
+    }
+    if (seq < 0) return;
+    const int g = blockIdx.y;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars->q_full), 1);
+        for (int s = 0; s < KV_STAGES; s++) {
+            mbar_init(smem_u32(&bars->k_full[s]), 1);
+            mbar_init(smem_u32(&bars->k_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_full[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 1);
+        }
+        for (int x = 0; x < 2; x++) {
+            mbar_init(smem_u32(&bars->s_full[x]), 1);
+            mbar_init(smem_u32(&bars->p_ready[x]), 4);
+            mbar_init(smem_u32(&bars->pv_done[x]), 1);
+        }
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+
+    const int t_first = b.cu_seqlens[seq];
+    const int qlen = b.cu_seqlens[seq + 1] - t_first;
+    const int slot = b.slots[seq];
+    const int len0 = b.lengths[slot];
+    // per tile: tokens [tq0 + x TQ, +nq), positions from pos0, key blocks [lo_blk, hi_blk)
+    int nq[2], pos0[2], lo_blk[2], hi_blk[2];
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+        nq[x] = min(TQ, qlen - (tq0 + x * TQ));
+        pos0[x] = len0 + tq0 + x * TQ;
+        if (nq[x] > 0) {
+            const int first_lo = (window > 0 && pos0[x] - window + 1 > 0) ? pos0[x] - window + 1 : 0;
+            lo_blk[x] = first_lo / KEYS;
+            hi_blk[x] = (pos0[x] + nq[x] - 1) / KEYS + 1;
+        } else {
+            lo_blk[x] = 0;
+            hi_blk[x] = 0;
+        }
+    }
+    const int blk0 = nq[1] > 0 ? min(lo_blk[0], lo_blk[1]) : lo_blk[0];
+    const int blk1 = max(hi_blk[0], hi_blk[1]);
+    const int n_iter = blk1 - blk0;
+    const int last_page = (len0 + min(qlen, tq0 + 2 * TQ) - 1) / PAGE;
+    const int* pt = page_table + (size_t)slot * max_pages;
+    auto active = [&](int x, int j) { return blk0 + j >= lo_blk[x] && blk0 + j < hi_blk[x]; };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * 2 * 128 * rep * TQ));
+#pragma unroll
+            for (int x = 0; x < 2; x++) {                                // rows beyond the batch are filled with zeros
+                tma_load_3d(qs + x * TILE_BYTES, &map_q, 0, g * rep, t_first + tq0 + x * TQ, smem_u32(&bars->q_full));
+                tma_load_3d(qs + x * TILE_BYTES + HALF_BYTES, &map_q, 64, g * rep, t_first + tq0 + x * TQ, smem_u32(&bars->q_full));
+            }
+            for (int j = 0; j < n_iter; j++) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+                int pg[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    int pi = (blk0 + j) * 2 + h;
+                    if (pi > last_page) pi = last_page;
+                    int page = pt[pi];
+                    if (page < 0 || page >= n_pages_pool) { gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi); page = 0; }
+                    pg[h] = page;
+                }
+                if (!mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+                mbar_expect_tx(smem_u32(&bars->k_full[s]), TILE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int row = (pg[h] * G + g) * PAGE;
+                    tma_load_2d(ks + s * TILE_BYTES + h * (PAGE * 128), &map_k, 0, row, smem_u32(&bars->k_full[s]));
+                    tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
+                }
+                if (!mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag, status, 2)) break;
+                mbar_expect_tx(smem_u32(&bars->v_full[s]), TILE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int row = (pg[h] * G + g) * PAGE;
+                    tma_load_2d(vs + s * TILE_BYTES + h * (PAGE * 128), &map_v, 0, row, smem_u32(&bars->v_full[s]));
+                    tma_load_2d(vs + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_v, 64, row, smem_u32(&bars->v_full[s]));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16(ROWS, KEYS, 0);
+            constexpr uint32_t idesc_o = idesc_bf16(ROWS, D, 1);
+            uint32_t n_pv[2] = {0, 0};                                   // P V products issued per tile
+            bool ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag, status, 5);
+            auto issue_s = [&](int x, int j) {                           // K stage of block j is known to be loaded
+                const int s = j % KV_STAGES;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint32_t off = (k >> 2) * HALF_BYTES;
+                    umma_ss(tmem + 128 * x, desc_kmajor(qs + x * TILE_BYTES + off) + 2 * (k & 3),
+                            desc_kmajor(ks + s * TILE_BYTES + off) + 2 * (k & 3), idesc_s, k != 0);
+                }
+                umma_commit(smem_u32(&bars->s_full[x]));
+            };
+            auto k_ready = [&](int j) {
+                return mbar_wait(smem_u32(&bars->k_full[j % KV_STAGES]), (uint32_t)(j / KV_STAGES) & 1u, abort_flag, status, 3);
+            };
+            if (ok && n_iter > 0) {
+                ok = k_ready(0);
+                if (ok) {
+                    tc_fence_after();
+                    if (active(0, 0)) issue_s(0, 0);
+                    if (active(1, 0)) issue_s(1, 0);
+                    umma_commit(smem_u32(&bars->k_empty[0]));
+                }
+            }
+            for (int j = 0; j < n_iter && ok; j++) {
+                const int s = j % KV_STAGES;
+                bool k_next = false;                                     // whether K of block j + 1 has been waited for
+                ok = mbar_wait(smem_u32(&bars->v_full[s]), (uint32_t)(j / KV_STAGES) & 1u, abort_flag, status, 6);
+#pragma unroll
+                for (int x = 0; x < 2 && ok; x++) {
+                    if (active(x, j)) {
+                        ok = mbar_wait(smem_u32(&bars->p_ready[x]), n_pv[x] & 1u, abort_flag, status, 7);
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < 8; kk++)                   // 16 keys per MMA: 8 columns of P, 2 KB of V
+                            umma_ts(tmem + 256 + 128 * x, tmem + 128 * x + kk * 8,
+                                    desc_mnmajor(vs + s * TILE_BYTES + kk * 2048), idesc_o, (n_pv[x] | (uint32_t)kk) != 0);
+                        umma_commit(smem_u32(&bars->pv_done[x]));
+                        n_pv[x]++;
+                    }
+                    if (j + 1 < n_iter && active(x, j + 1)) {            // the tile's next scores, behind its P V
+                        if (!k_next) { ok = k_ready(j + 1); k_next = true; if (!ok) break; tc_fence_after(); }
+                        issue_s(x, j + 1);
+                    }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&bars->v_empty[s]));
+                if (j + 1 < n_iter) {
+                    if (!k_next) { ok = k_ready(j + 1); if (!ok) break; }
+                    umma_commit(smem_u32(&bars->k_empty[(j + 1) % KV_STAGES]));
+                }
+            }
+        }
+    } else {
+        const int x = (warp - 2) >> 2;                                   // warps 2..5: tile 0, warps 6..9: tile 1
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+        const uint32_t col_s = 128 * x, col_o = 256 + 128 * x;
+        const int tq = r / rep;
+        const bool row_ok = tq < nq[x];
+        const int row_pos = pos0[x] + tq;
+        const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+        const int first_lo = (window > 0 && pos0[x] - window + 1 > 0) ? pos0[x] - window + 1 : 0;
+        float m_run = -INFINITY, l_run = 0.f;
+        uint32_t n_done = 0;                                             // blocks of this tile finished
+        bool ok = true;
+        for (int j = 0; j < n_iter && ok; j++) {
+            if (!active(x, j)) continue;
+            const int key0 = (blk0 + j) * KEYS;
+            ok = mbar_wait(smem_u32(&bars->s_full[x]), n_done & 1u, abort_flag, status, 8);
+            if (!ok) break;
+            tc_fence_after();
+            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < first_lo || window > 0 || nq[x] * rep < ROWS;
+            float v[4][32];
+            tmem_ld_row128(lane_base + col_s, v);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int kj = key0 + c * 32 + i;
+                        if (!(row_ok && kj <= row_pos && kj >= row_lo)) v[c][i] = -INFINITY;
+                    }
+            }
+            float mx4[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                mx4[c] = v[c][0];
+#pragma unroll
+                for (int i = 1; i < 32; i++) mx4[c] = fmaxf(mx4[c], v[c][i]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float m_new = m_run;                                         // lazy reference maximum, as in the one-tile kernel
+            if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * scale_log2e > 8.f)) m_new = mx;
+            const float corr = (m_run == -INFINITY) ? 0.f : (m_new == m_run ? 1.f : fast_exp2((m_run - m_new) * scale_log2e));
+            const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
+            // P over the first half of this tile's own scores: all of this row's scores are in registers by now,
+            // and a thread only ever touches its own row (lane) of tensor memory
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(fmaf(v[c][i], scale_log2e, mneg));
+                    float p1 = fast_exp2(fmaf(v[c][i + 1], scale_log2e, mneg));
+                    rs4[c] += p0 + p1;
+                    pk[i >> 1] = pack2(p0, p1);
+                }
+                tmem_st16(lane_base + col_s + c * 16, pk);
+            }
+            if (n_done > 0) {                                            // O follows the reference maximum, rarely
+                ok = mbar_wait(smem_u32(&bars->pv_done[x]), (n_done - 1u) & 1u, abort_flag, status, 9);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        float o[32];
+                        tmem_ld32(lane_base + col_o + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] *= corr;
+                        tmem_st32(lane_base + col_o + c * 32, o);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready[x]));
+            l_run = l_run * corr + (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            m_run = m_new;
+            n_done++;
+        }
+        if (ok && n_done > 0) ok = mbar_wait(smem_u32(&bars->pv_done[x]), (n_done - 1u) & 1u, abort_flag, status, 10);
+        if (ok && n_done > 0) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const int head = g * rep + (r - tq * rep);
+            __nv_bfloat16* dst = out + ((size_t)(t_first + tq0 + x * TQ + tq) * H + head) * D;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                float v[32];
+                tmem_ld32(lane_base + col_o + c * 32, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 pk;
+                        pk.x = pack2(v[i] * inv, v[i + 1] * inv); pk.y = pack2(v[i + 2] * inv, v[i + 3] * inv);
+                        pk.z = pack2(v[i + 4] * inv, v[i + 5] * inv); pk.w = pack2(v[i + 6] * inv, v[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 50000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -477,11 +823,12 @@ EncodeTiledFn encode_fn() {
 }  // namespace
 
 // Causal attention for runs of new tokens on tcgen05; head_dim 128, pages of 64, at most 8 heads per group
-// with 128 % (heads per group) == 0.
+// with 128 % (heads per group) == 0.  tiles: query tiles of 128 rows per block, 1 or 2, or 0 to let the
+// function choose by the amount of work.
 GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                 int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                 const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
-                                int* status, cudaStream_t stream) {
+                                int tiles, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (page_size != PAGE || d != D) return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim %d", PAGE, D);
     if (G <= 0 || H % G) return gfb_fail("gfb_attn_prefill_tc: %d heads over %d groups", H, G);
@@ -512,15 +859,38 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
         if (r != CUDA_SUCCESS) return gfb_fail("gfb_attn_prefill_tc: tensor map of the cache refused (%d)", (int)r);
     }
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
-    size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
-        configured = smem;
+    if (tiles < 0 || tiles > 2) return gfb_fail("gfb_attn_prefill_tc: %d query tiles per block (0 = choose, 1 or 2)", tiles);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
     }
-    dim3 grid((n_tokens + TQ - 1) / TQ + n_seqs, G);
-    cudaError_t e = gfb_launch(attn_prefill_tc_kernel, grid, dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                               page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
+    cudaError_t e;
+    const long blocks2 = ((long)(n_tokens + 2 * TQ - 1) / (2 * TQ)) * G;
+    if (tiles == 2 || (tiles == 0 && blocks2 >= 2L * sms)) {
+        // enough work for two rounds of blocks of two tiles, which share their K/V loads and keep the tensor
+        // pipe busier; with fewer blocks the finer grain of the one-tile kernel balances the SMs better
+        size_t smem = 1024 + (size_t)(2 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars2);
+        static size_t configured2 = 0;
+        if (smem > configured2) {
+            cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
+            configured2 = smem;
+        }
+        dim3 grid((n_tokens + 2 * TQ - 1) / (2 * TQ) + n_seqs, G);
+        e = gfb_launch(attn_prefill_tc2_kernel, grid, dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
+    } else {
+        size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
+        static size_t configured = 0;
+        if (smem > configured) {
+            cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
+            configured = smem;
+        }
+        dim3 grid((n_tokens + TQ - 1) / TQ + n_seqs, G);
+        e = gfb_launch(attn_prefill_tc_kernel, grid, dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
+    }
     return gfb_check(e, "gfb_attn_prefill_tc");
 }

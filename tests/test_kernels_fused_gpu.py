@@ -77,18 +77,22 @@ PREFILL_CASES = [  # H, G, d, q_lens, starts
     (6, 2, 64, [45, 3, 129], [5, 64, 100]),           # 3 heads per group: 42 tokens per tile, 2 idle rows
     (5, 5, 128, [260], [0]),                          # one head per group: 128 tokens per tile
     (16, 2, 128, [33, 64], [1000, 7]),                # 8 heads per group
+    (32, 8, 128, [700], [0]),                         # many key blocks per tile, from position 0
+    (8, 2, 128, [300, 150, 64], [500, 1000, 129]),    # long contexts: blocks far below the diagonal
 ]
 
 
+@pytest.mark.parametrize("tiles", [1, 2])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("H,G,d,q_lens,starts", PREFILL_CASES)
-def test_attention_bf16_prefill(window, H, G, d, q_lens, starts):
+def test_attention_bf16_prefill(tiles, window, H, G, d, q_lens, starts):
+    """tiles: query tiles per block of the tcgen05 kernel (head_dim 128); the other kernels ignore it."""
     batch, table, n_pages = make_batch(q_lens, starts, 5, 64, 24, seed=3)
     T, dt = batch.n_tokens, torch.bfloat16
     kv = PagedKV(rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5), table, 64)
     q = rnd(T, H, d, dtype=dt, seed=6)
     out, ref = torch.empty(T, H * d, dtype=dt, device=DEV), torch.empty(T, H * d, dtype=dt, device=DEV)
-    ops.attention(q, kv, batch, out, H, G, d, 1 / math.sqrt(d), window)
+    ops.kernels()._attention_bf16(q, kv, batch, out, H, G, d, 1 / math.sqrt(d), window, prefill=True, tiles=tiles)
     REF.attention(q, kv, batch, ref, H, G, d, 1 / math.sqrt(d), window)
     ops.check_status(batch.status)
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
@@ -107,14 +111,15 @@ def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal():
     for pos in (3, 200):
         k[int(table[slot, pos // 64]), :, pos % 64, 0] = 30.0 if pos == 3 else 60.0
     kv = PagedKV(k, v, table, 64)
-    out = torch.empty(300, H * d, dtype=dt, device=DEV)
-    ops.attention(q, kv, batch, out, H, G, d, 1.0, None)
     v3 = v[int(table[slot, 0]), :, 3].repeat_interleave(H // G, dim=0).reshape(H * d).float()
     v200 = v[int(table[slot, 200 // 64]), :, 200 % 64].repeat_interleave(H // G, dim=0).reshape(H * d).float()
-    for t in (3, 64, 199):
-        torch.testing.assert_close(out[t].float(), v3, rtol=1e-2, atol=1e-2)
-    for t in (200, 299):
-        torch.testing.assert_close(out[t].float(), v200, rtol=1e-2, atol=1e-2)
+    for tiles in (1, 2):
+        out = torch.empty(300, H * d, dtype=dt, device=DEV)
+        ops.kernels()._attention_bf16(q, kv, batch, out, H, G, d, 1.0, None, prefill=True, tiles=tiles)
+        for t in (3, 64, 199):
+            torch.testing.assert_close(out[t].float(), v3, rtol=1e-2, atol=1e-2)
+        for t in (200, 299):
+            torch.testing.assert_close(out[t].float(), v200, rtol=1e-2, atol=1e-2)
 
 
 @pytest.mark.parametrize("H,G,d,q_lens,starts", [(32, 8, 128, [200, 31], [0, 77]), (6, 2, 24, [64, 70], [3, 0]), (4, 4, 16, [130], [60])])
