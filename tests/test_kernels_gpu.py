@@ -299,7 +299,9 @@ def test_sample_frequencies_follow_softmax():
 
 # ---- tensor-core product (tcgen05 + TMA) -------------------------------------------------
 TC_SHAPES = [(1, 384, 144), (8, 512, 256), (5, 320, 144), (16, 1024, 4096), (17, 6144, 512), (64, 768, 2048),
-             (100, 1008, 200), (128, 256, 64), (129, 512, 1024), (300, 640, 456), (256, 2048, 4096), (1000, 4352, 512), (2048, 1024, 1024)]
+             (100, 1008, 200), (128, 256, 64), (129, 512, 1024), (300, 640, 456), (256, 2048, 4096), (1000, 4352, 512), (2048, 1024, 1024),
+             # more 256 x 256 tiles than pairs of SMs, not a multiple of them, ragged rows and K
+             (2048, 4096, 512), (600, 7680, 456), (300, 28672, 192), (2048, 6144, 1024)]
 
 
 @pytest.mark.parametrize("mode", ["store", "store32", "add", "swiglu"])
