@@ -216,3 +216,31 @@ def test_fused_decode_attention_sees_the_new_token_and_a_far_key():
     for h in range(H):
         torch.testing.assert_close(out[0, h * d:(h + 1) * d].float(), new_v[h // (H // G)], rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(out[1, h * d:(h + 1) * d].float(), v_pool[far_page, h // (H // G), 9].float(), rtol=2e-2, atol=2e-2)
+
+
+def test_decode_attention_of_a_large_batch():
+    """64 sequences at scattered positions (several blocks per SM): the fused and the plain entry of the decode
+    kernel against the plain implementation."""
+    H, G, d = 32, 8, 128
+    n = 64
+    starts = [(37 * i) % 300 for i in range(n)]
+    batch, table, n_pages = make_batch([1] * n, starts, n + 3, 64, 8, seed=5)
+    dt = torch.bfloat16
+    W = (H + 2 * G) * d
+    rt = torch.empty(8 * 64, d // 2, 2, device=DEV)
+    ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).to(DEV), rt)
+    k0, v0 = rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5)
+    kv, kv_ref = PagedKV(k0.clone(), v0.clone(), table, 64), PagedKV(k0.clone(), v0.clone(), table, 64)
+    partials = rnd(3, n, W, seed=1)
+    scale = 1 / math.sqrt(d)
+    out, ref = torch.empty(n, H * d, dtype=dt, device=DEV), torch.empty(n, H * d, dtype=dt, device=DEV)
+    assert ops.kernels().rope_append_attention(None, partials, kv, batch, rt, out, H, G, d, "interleaved", True, scale, None)
+    q_ref = torch.empty(n, H, d, dtype=dt, device=DEV)
+    REF.rope_append(None, q_ref, kv_ref, batch, rt, H, G, d, "interleaved", True, partials)
+    REF.attention(q_ref, kv_ref, batch, ref, H, G, d, scale, None)
+    ops.check_status(batch.status)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
+    torch.testing.assert_close(kv.k_pool.float(), kv_ref.k_pool.float(), rtol=2e-2, atol=2e-2)
+    out2 = torch.empty_like(out)
+    ops.kernels()._attention_bf16(q_ref, kv_ref, batch, out2, H, G, d, scale, None, splits=1)
+    torch.testing.assert_close(out2.float(), ref.float(), rtol=2e-2, atol=1e-2)
