@@ -20,6 +20,7 @@ constexpr int PAGE = 64;
 constexpr int THREADS = 128;
 constexpr int MAX_REP = 8;          // query heads per key/value head
 constexpr int MAX_DPT = 2;          // head_dim <= THREADS * MAX_DPT
+constexpr int DECODE_NBUF = 3;      // K/V tile pairs of the tensor-core decode kernel: NBUF - 1 pages in flight per block
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -293,7 +294,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     constexpr int TILE = PAGE * PITCH;           // elements per tile
     extern __shared__ __align__(16) uint8_t smem[];
     __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1
-    __nv_bfloat16* qs = tiles + 4 * TILE;                      // [8][PITCH]
+    __nv_bfloat16* qs = tiles + 2 * DECODE_NBUF * TILE;        // [8][PITCH]
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int rep = H / G;
@@ -327,8 +328,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
             cp_async16(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8);
         }
     };
-    if (p0 < p1) issue(p0, 0);                                 // in flight while q is prepared
-    cp_async_commit();
+    // DECODE_NBUF - 1 pages in flight while q is prepared and, later, while a page is worked on
+#pragma unroll
+    for (int a = 0; a < DECODE_NBUF - 1; a++) {
+        if (p0 + a < p1) issue(p0 + a, a);
+        cp_async_commit();
+    }
     // SRC != SRC_Q: the new key and value of this token, kept in registers by the threads that made them.  The
     // slice that owns the last page patches them into its shared-memory copy of that page: the page may have
     // been read before the store to the cache landed.
@@ -423,10 +428,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     const int mid = lane >> 3, mr = lane & 7;                  // ldmatrix: this lane addresses row mr of matrix mid
 
     for (int p = p0; p < p1; p++) {
-        const int buf = (p - p0) & 1;
-        if (p + 1 < p1) issue(p + 1, buf ^ 1);
+        const int buf = (p - p0) % DECODE_NBUF;
+        if (p + DECODE_NBUF - 1 < p1) issue(p + DECODE_NBUF - 1, (p - p0 + DECODE_NBUF - 1) % DECODE_NBUF);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<DECODE_NBUF - 1>();
         __syncthreads();
         if (SRC != SRC_Q && p == last_page) {                  // uniform: the block's last page holds the new token
             if (patch) {
@@ -769,7 +774,7 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
         {attn_decode_mma_kernel<128, SRC_Q>, attn_decode_mma_kernel<128, SRC_QKV>, attn_decode_mma_kernel<128, SRC_PARTIALS>}};
     static bool configured[2][3] = {{false, false, false}, {false, false, false}};
     const int di = d == 128 ? 1 : 0;
-    const size_t msmem = (size_t)(4 * PAGE + 8) * (d + 8) * 2;
+    const size_t msmem = (size_t)(2 * DECODE_NBUF * PAGE + 8) * (d + 8) * 2;
     Kern kern = kerns[di][src];
     if (msmem > 48 * 1024 && !configured[di][src]) {
         cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem);

@@ -233,14 +233,14 @@ class CudaKernels:
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         """Into how many slices a decode step cuts each sequence's cache (`blocks` = tokens x key/value heads, the
         blocks of one slice).  A simple cost model fitted to measurements on a B200 (contexts of 600 to 32,000,
-        batches of 1 to 64): three blocks fit on an SM, so blocks * slices run in ceil(blocks * slices / (3 SMs))
-        rounds; a round costs the pages of a slice plus about two pages' worth of fixed work per block; a slice
+        batches of 1 to 64): two blocks fit on an SM, so blocks * slices run in ceil(blocks * slices / (2 SMs))
+        rounds; a round costs the pages of a slice plus about four pages' worth of fixed work per block; a slice
         keeps at least 4 pages.  The cheapest count wins, the smaller one on ties."""
         pages = -(-max(max_kv_len, 1) // page_size)
-        cap = 3 * self.sm_count
+        cap = 2 * self.sm_count
         best, best_cost = 1, None
         for s in range(1, max(1, min(pages // 4, 48)) + 1):
-            cost = -(-blocks * s // cap) * (pages / s + 2.0)
+            cost = -(-blocks * s // cap) * (pages / s + 4.0)
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best
