@@ -219,6 +219,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// two 32-bit lanes per instruction (sm_100): r = a * b + c and r = a + b on pairs; the maximum of three
+__device__ __forceinline__ void fma2(float a0, float a1, float b, float c, float& r0, float& r1) {
+    unsigned long long pa, pb, pc, pr;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(pb) : "f"(b));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(pc) : "f"(c));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(pr) : "l"(pa), "l"(pb), "l"(pc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r0), "=f"(r1) : "l"(pr));
+}
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+    unsigned long long pa, pb;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(pb) : "f"(b0), "f"(b1));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(pa) : "l"(pa), "l"(pb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(pa));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -404,9 +425,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float mx4[4];                                                // four chains instead of one of 128
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                mx4[c] = v[c][0];
+                mx4[c] = fmaxf(v[c][0], v[c][1]);
 #pragma unroll
-                for (int i = 1; i < 32; i++) mx4[c] = fmaxf(mx4[c], v[c][i]);
+                for (int i = 2; i < 32; i += 2) mx4[c] = max3(mx4[c], v[c][i], v[c][i + 1]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // The running maximum only has to keep the exponentials in range, so it follows the true maximum
@@ -422,13 +443,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 uint32_t pk[16];
+                float rs_odd = 0.f;                                      // rs4[c] and rs_odd: one packed sum
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(v[c][i], scale_log2e, mneg));
-                    float p1 = fast_exp2(fmaf(v[c][i + 1], scale_log2e, mneg));
-                    rs4[c] += p0 + p1;
+                    float t0, t1;
+                    fma2(v[c][i], v[c][i + 1], scale_log2e, mneg, t0, t1);
+                    const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                    add2(rs4[c], rs_odd, p0, p1);
                     pk[i >> 1] = pack2(p0, p1);
                 }
+                rs4[c] += rs_odd;
                 tmem_st16(lane_base + COL_P + sb * 64 + c * 16, pk);
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
@@ -723,9 +747,9 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             float mx4[4];
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                mx4[c] = v[c][0];
+                mx4[c] = fmaxf(v[c][0], v[c][1]);
 #pragma unroll
-                for (int i = 1; i < 32; i++) mx4[c] = fmaxf(mx4[c], v[c][i]);
+                for (int i = 2; i < 32; i += 2) mx4[c] = max3(mx4[c], v[c][i], v[c][i + 1]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float m_new = m_run;                                         // lazy reference maximum, as in the one-tile kernel
@@ -738,13 +762,16 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 uint32_t pk[16];
+                float rs_odd = 0.f;                                      // rs4[c] and rs_odd: one packed sum
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(v[c][i], scale_log2e, mneg));
-                    float p1 = fast_exp2(fmaf(v[c][i + 1], scale_log2e, mneg));
-                    rs4[c] += p0 + p1;
+                    float t0, t1;
+                    fma2(v[c][i], v[c][i + 1], scale_log2e, mneg, t0, t1);
+                    const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                    add2(rs4[c], rs_odd, p0, p1);
                     pk[i >> 1] = pack2(p0, p1);
                 }
+                rs4[c] += rs_odd;
                 tmem_st16(lane_base + col_s + c * 16, pk);
             }
             if (n_done > 0) {                                            // O follows the reference maximum, rarely
