@@ -77,3 +77,35 @@ def test_8b_layer_sizes_greedy_tokens_agree_between_precisions(big):
     first = sum(a[20] == b[20] for a, b in zip(out["float32"], out["bfloat16"]))
     assert first == len(prompts)                     # the first new token agrees; later ones may fork on near-ties
     assert same >= 1
+
+
+def test_long_prompt_and_decoding_behind_it():
+    """A 4,800-token prompt (the prefill attention takes two query tiles per block from about 4,700 tokens on at
+    these head counts, and a decode step behind it cuts the cache into many slices), one layer of 16 heads in
+    8 groups with head_dim 128: the last places of the prompt and four decoded places against the plain
+    implementation, judged like the test above."""
+    cfg = gf.config_from_name("llama-3.1-8b")
+    cfg.update(hidden_size=2048, num_attention_heads=16, num_key_value_heads=8, intermediate_size=1024,
+               num_hidden_layers=1, vocab_size=512, max_position_embeddings=8192)
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        gf.write_model_folder(d, cfg, seed=11)
+        p, pc = plain_llama.load_folder(d)
+        toks = traces.make_requests(cfg["vocab_size"], [4804], seed=2)["r0"]
+        want = plain_llama.forward(toks, p, pc)[-8:]
+        noise = plain_llama.forward(toks, p, pc, act=torch.bfloat16)[-8:] - want
+        model = gf.load(d, dtype="bfloat16", device="cuda")
+        with torch.no_grad():
+            cache = model.new_cache(max_tokens=4864, max_seqs=1)
+            st = gf.Stepper(model, cache)
+            slot = cache.begin(1)
+            rows = [st.step(slot, [toks[:4800]], [[4796, 4797, 4798, 4799]]).cpu()]
+            for t in toks[4800:]:
+                rows.append(st.step(slot, [[t]], "last").cpu())
+            st.check()
+            cache.end(slot)
+        got = torch.cat(rows)
+        err = got - want
+        rms = lambda t: float(t.pow(2).mean().sqrt())
+        assert rms(err) <= 1.5 * rms(noise), f"rms error {rms(err):.4f}, bfloat16 noise {rms(noise):.4f}"
+        assert float(err.abs().max()) <= 2.0 * float(noise.abs().max())
