@@ -44,6 +44,22 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def decode_slices(max_kv_len: int, page_size: int, blocks: int, sm_count: int) -> int:
+    """Into how many slices a decode step cuts each sequence's cache (`blocks` = tokens x key/value heads, the
+    blocks of one slice).  A simple cost model fitted to measurements on a B200 (contexts of 600 to 32,000,
+    batches of 1 to 64): two blocks fit on an SM, so blocks * slices run in ceil(blocks * slices / (2 SMs))
+    rounds; a round costs the pages of a slice plus about four pages' worth of fixed work per block; a slice
+    keeps at least 4 pages.  The cheapest count wins, the smaller one on ties."""
+    pages = -(-max(max_kv_len, 1) // page_size)
+    cap = 2 * sm_count
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(pages // 4, 48)) + 1):
+        cost = -(-blocks * s // cap) * (pages / s + 4.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 class CudaKernels:
     """The operations of `ops`, bound to the sm_100a libraries.  A library is
     compiled and loaded when its first function is needed."""
@@ -231,19 +247,7 @@ class CudaKernels:
                    c_float(scale), c_int(window or 0), _ptr(batch.status), _stream())
 
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
-        """Into how many slices a decode step cuts each sequence's cache (`blocks` = tokens x key/value heads, the
-        blocks of one slice).  A simple cost model fitted to measurements on a B200 (contexts of 600 to 32,000,
-        batches of 1 to 64): two blocks fit on an SM, so blocks * slices run in ceil(blocks * slices / (2 SMs))
-        rounds; a round costs the pages of a slice plus about four pages' worth of fixed work per block; a slice
-        keeps at least 4 pages.  The cheapest count wins, the smaller one on ties."""
-        pages = -(-max(max_kv_len, 1) // page_size)
-        cap = 2 * self.sm_count
-        best, best_cost = 1, None
-        for s in range(1, max(1, min(pages // 4, 48)) + 1):
-            cost = -(-blocks * s // cap) * (pages / s + 4.0)
-            if best_cost is None or cost < best_cost - 1e-9:
-                best, best_cost = s, cost
-        return best
+        return decode_slices(max_kv_len, page_size, blocks, self.sm_count)
 
     def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None, tiles=0):
         T = batch.n_tokens

@@ -114,3 +114,18 @@ def test_bad_requests_are_refused(tiny):
     st.step(slots, [[1, 300], [2]])                                             # id 300 is outside tiny-a's vocabulary
     with pytest.raises(gf.ops.KernelError, match="token id out of range"):
         st.check()
+
+
+def test_decode_slice_count_follows_its_cost_model():
+    """How many slices a decode step cuts a sequence's cache into (a host-side decision, no GPU needed)."""
+    from gpt_fast_b200.ops.cuda import decode_slices
+    sms = 148
+    assert decode_slices(130, 64, 64, sms) == 1                      # three pages: nothing to cut
+    assert decode_slices(4001, 64, 64, sms) == 4                     # 64 blocks x 4 = one round of 256 blocks
+    assert decode_slices(32001, 64, 8, sms) == 37                    # one sequence: as many blocks as fit in one round
+    assert decode_slices(2001, 64, 512, sms) == 1                    # the grid is large already
+    for ctx in (1, 63, 64, 65, 1000, 5000, 100000):
+        for blocks in (1, 8, 64, 512, 4096):
+            s = decode_slices(ctx, 64, blocks, sms)
+            pages = -(-ctx // 64)
+            assert 1 <= s <= 48 and (s == 1 or pages // s >= 4)      # a slice keeps at least four pages
