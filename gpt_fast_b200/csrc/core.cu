@@ -88,13 +88,20 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float scratch[32];
-    __shared__ float part;
+    __shared__ float parts[NORM_CLUSTER];                       // every block's sum of squares, pushed here by its owner
+    // every block announces that it runs (its shared memory may be written from now on); the matching wait comes
+    // just before the first remote write and finds the barrier complete by then
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int r = blockIdx.y;
     const int chunk = D / NORM_CLUSTER;
-    const int c0 = (int)cluster.block_rank() * chunk;
+    const int rank = (int)cluster.block_rank();
+    const int c0 = rank * chunk;
     const size_t row = (size_t)r * D;
+    // the usual case (chunk <= 4 * blockDim): one float4 per thread, kept in registers between the two passes
+    const bool in_regs = chunk <= 4 * (int)blockDim.x;
+    float4 keep = make_float4(0.f, 0.f, 0.f, 0.f);
     float ss = 0.f;
     for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
         float4 v = *reinterpret_cast<const float4*>(x + row + i);
@@ -112,23 +119,26 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
             }
             *reinterpret_cast<float4*>(x + row + i) = v;
         }
+        keep = v;
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = gfb_block_sum(ss, scratch);
-    if (threadIdx.x == 0) part = ss;
+    // each block pushes its sum into every block's `parts`; after ONE cluster barrier all read only their own
+    // shared memory, so no block has to wait for the others before it leaves
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (threadIdx.x < NORM_CLUSTER) *cluster.map_shared_rank(&parts[rank], threadIdx.x) = ss;
     cluster.sync();
     float total = 0.f;
-    for (int k = 0; k < NORM_CLUSTER; k++) total += *cluster.map_shared_rank(&part, k);     // fixed order
+    for (int k = 0; k < NORM_CLUSTER; k++) total += parts[k];                                  // fixed order
     const float rstd = rsqrtf(total / (float)D + eps);
     for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
-        float4 v = *reinterpret_cast<const float4*>(x + row + i);
+        const float4 v = in_regs ? keep : *reinterpret_cast<const float4*>(x + row + i);
         TO* o = out + row + i;
         o[0] = gfb_from_f32<TO>(v.x * rstd * gfb_to_f32(w[i]));
         o[1] = gfb_from_f32<TO>(v.y * rstd * gfb_to_f32(w[i + 1]));
         o[2] = gfb_from_f32<TO>(v.z * rstd * gfb_to_f32(w[i + 2]));
         o[3] = gfb_from_f32<TO>(v.w * rstd * gfb_to_f32(w[i + 3]));
     }
-    cluster.sync();                 // no block leaves while another may still read its `part`
 }
 
 // One block per row with the row held in registers: a single pass over x (float4 loads),
