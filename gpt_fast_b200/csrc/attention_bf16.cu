@@ -253,7 +253,7 @@ struct RopeSource {
 };
 
 // x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
-// sums in ascending order.  The loads of four partial sums (8 N values) are in flight together; a pair that is
+// sums in ascending order.  The loads of eight partial sums (16 N values) are in flight together; a pair that is
 // not wanted repeats a wanted one's addresses, so no branch sits between the loads.
 template <int SRC, int N>
 __device__ __forceinline__ void load_pairs(const RopeSource& r, const size_t* e0, const size_t* e1, float* x0, float* x1) {
@@ -261,16 +261,17 @@ __device__ __forceinline__ void load_pairs(const RopeSource& r, const size_t* e0
         const float* p = (const float*)r.src;
 #pragma unroll
         for (int i = 0; i < N; i++) { x0[i] = 0.f; x1[i] = 0.f; }
-        for (int k = 0; k < r.S; k += 4) {
-            float a[4][N], c[4][N];
+        constexpr int W = 8;                                  // partial sums in flight together
+        for (int k = 0; k < r.S; k += W) {
+            float a[W][N], c[W][N];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < W; u++) {
                 const float* pk = p + (size_t)min(k + u, r.S - 1) * r.slice;
 #pragma unroll
                 for (int i = 0; i < N; i++) { a[u][i] = pk[e0[i]]; c[u][i] = pk[e1[i]]; }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < W; u++)
                 if (k + u < r.S) {
 #pragma unroll
                     for (int i = 0; i < N; i++) { x0[i] += a[u][i]; x1[i] += c[u][i]; }
