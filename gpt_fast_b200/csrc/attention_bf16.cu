@@ -20,7 +20,9 @@ constexpr int PAGE = 64;
 constexpr int THREADS = 128;
 constexpr int MAX_REP = 8;          // query heads per key/value head
 constexpr int MAX_DPT = 2;          // head_dim <= THREADS * MAX_DPT
-constexpr int DECODE_NBUF = 3;      // K/V tile pairs of the tensor-core decode kernel: NBUF - 1 pages in flight per block
+// K/V tile pairs of the tensor-core decode kernel: NBUF - 1 pages are in flight per block.  3 lets two blocks share
+// an SM; 5 (one block per SM) is for small grids, where a short context is then requested all at once.
+constexpr int DECODE_NBUF_MANY = 3, DECODE_NBUF_FEW = 5;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -284,7 +286,7 @@ __device__ __forceinline__ void load_pairs(const RopeSource& r, const size_t* e0
     }
 }
 
-template <int D, int SRC>
+template <int D, int SRC, int DECODE_NBUF>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
@@ -770,20 +772,33 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
                               RopeSource rs) {
     typedef void (*Kern)(const __nv_bfloat16*, __nv_bfloat16*, float*, float*, GfbPagedKV, GfbBatch, int, int, float, int, int,
                          int*, RopeSource);
-    static const Kern kerns[2][3] = {
-        {attn_decode_mma_kernel<64, SRC_Q>, attn_decode_mma_kernel<64, SRC_QKV>, attn_decode_mma_kernel<64, SRC_PARTIALS>},
-        {attn_decode_mma_kernel<128, SRC_Q>, attn_decode_mma_kernel<128, SRC_QKV>, attn_decode_mma_kernel<128, SRC_PARTIALS>}};
-    static bool configured[2][3] = {{false, false, false}, {false, false, false}};
+    static const Kern kerns[2][2][3] = {
+        {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_MANY>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_MANY>,
+          attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_MANY>},
+         {attn_decode_mma_kernel<128, SRC_Q, DECODE_NBUF_MANY>, attn_decode_mma_kernel<128, SRC_QKV, DECODE_NBUF_MANY>,
+          attn_decode_mma_kernel<128, SRC_PARTIALS, DECODE_NBUF_MANY>}},
+        {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_FEW>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_FEW>,
+          attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_FEW>},
+         {attn_decode_mma_kernel<128, SRC_Q, DECODE_NBUF_FEW>, attn_decode_mma_kernel<128, SRC_QKV, DECODE_NBUF_FEW>,
+          attn_decode_mma_kernel<128, SRC_PARTIALS, DECODE_NBUF_FEW>}}};
+    static bool configured[2][2][3] = {};
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+    }
     const int di = d == 128 ? 1 : 0;
-    const size_t msmem = (size_t)(2 * DECODE_NBUF * PAGE + 8) * (d + 8) * 2;
-    Kern kern = kerns[di][src];
-    if (msmem > 48 * 1024 && !configured[di][src]) {
+    const int few = (long)grid.x * grid.y * grid.z <= sms ? 1 : 0;      // at most one block per SM anyway
+    const int nbuf = few ? DECODE_NBUF_FEW : DECODE_NBUF_MANY;
+    const size_t msmem = (size_t)(2 * nbuf * PAGE + 8) * (d + 8) * 2;
+    Kern kern = kerns[few][di][src];
+    if (msmem > 48 * 1024 && !configured[few][di][src]) {
         cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem);
         if (a != cudaSuccess) {
             gfb_fail("decode attention: %zu bytes of shared memory refused: %s", msmem, cudaGetErrorString(a));
             return cudaErrorInvalidValue;
         }
-        configured[di][src] = true;
+        configured[few][di][src] = true;
     }
     gfb_error_text[0] = 0;
     return gfb_launch(kern, grid, dim3(THREADS), msmem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b,
