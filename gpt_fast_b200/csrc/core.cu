@@ -143,7 +143,7 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
 
 // One block per row with the row held in registers: a single pass over x (float4 loads),
 // packed stores.  For D % 4 == 0 and D <= 4 * VEC_MAX * blockDim.
-constexpr int NORM_VEC_MAX = 4;
+constexpr int NORM_VEC_MAX = 8;
 
 template <typename TW, typename TO>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
@@ -204,7 +204,10 @@ GFB_API int gfb_rmsnorm(float* x, const float* pending, int S, long slice, const
     }
     int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
     if (pending == nullptr && D % 4 == 0 && D <= 4 * NORM_VEC_MAX * threads) {
-#define VLAUNCH(TW, TO) e = gfb_launch(rmsnorm_vec_kernel<TW, TO>, dim3(R), dim3(threads), 0, stream, (const float*)x, (const TW*)w, (TO*)out, rows, D, eps)
+        // few threads with many loads each: more rows are resident per SM and every thread has 8 loads in flight
+        int vthreads = ((D / 4 + NORM_VEC_MAX - 1) / NORM_VEC_MAX + 31) / 32 * 32;
+        if (vthreads < 64) vthreads = 64;
+#define VLAUNCH(TW, TO) e = gfb_launch(rmsnorm_vec_kernel<TW, TO>, dim3(R), dim3(vthreads), 0, stream, (const float*)x, (const TW*)w, (TO*)out, rows, D, eps)
         if (w_dt == GFB_BF16 && out_dt == GFB_BF16) VLAUNCH(__nv_bfloat16, __nv_bfloat16);
         else if (w_dt == GFB_F32 && out_dt == GFB_BF16) VLAUNCH(float, __nv_bfloat16);
         else if (w_dt == GFB_BF16 && out_dt == GFB_F32) VLAUNCH(__nv_bfloat16, float);
@@ -335,16 +338,19 @@ __global__ void rope_append_kernel(const void* __restrict__ src_any, int S, size
 
 // Fast path for many tokens: bfloat16 qkv, interleaved pairs, head_dim % 8 == 0.  One thread moves
 // 8 elements (4 pairs): a 16-byte load of qkv, two 16-byte loads of (cos, sin), a 16-byte store.
-__global__ void rope_append_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
-                                       GfbPagedKV kv, GfbBatch b, const float* __restrict__ table, int table_len,
-                                       int H, int G, int d, int append, int* status) {
+constexpr int ROPE_VEC_ITEMS = 4;
+
+__global__ void __launch_bounds__(256)
+rope_append_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                       GfbPagedKV kv, GfbBatch b, const float* __restrict__ table, int table_len,
+                       int H, int G, int d, int append, int* status) {
     gfb_pdl_launch();
     gfb_pdl_wait();
+    // one block per token: the chain token -> sequence -> slot -> position -> page is walked once per block, and a
+    // thread's items (8 elements each, up to ROPE_VEC_ITEMS of them) are loaded together
     const int t = blockIdx.x;
     const int d8 = d >> 3;
     const int n_items = (H + (append ? 2 * G : 0)) * d8;
-    const int item = blockIdx.y * blockDim.x + threadIdx.x;
-    if (item >= n_items) return;
     const int s = b.tok_seq[t];
     const int slot = b.slots[s];
     const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
@@ -356,29 +362,49 @@ __global__ void rope_append_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __
         if (page < 0 || page >= kv.n_pages) ok = false;
         else cache_base = ((size_t)page * G * kv.page_size + off) * d;
     }
-    const int head = item / d8, c = item - head * d8;          // head over q, k, v; c: which 8 elements
     if (!ok) {
-        if (item == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
-        if (head < H) *reinterpret_cast<uint4*>(q_out + ((size_t)t * H + head) * d + c * 8) = make_uint4(0, 0, 0, 0);
+        if (threadIdx.x == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+        for (int item = threadIdx.x; item < H * d8; item += blockDim.x)
+            *reinterpret_cast<uint4*>(q_out + (size_t)t * H * d + (size_t)item * 8) = make_uint4(0, 0, 0, 0);
         return;
     }
-    uint4 raw = *reinterpret_cast<const uint4*>(qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d + c * 8);
-    __nv_bfloat16* dst;
-    if (head < H) dst = q_out + ((size_t)t * H + head) * d;
-    else if (head < H + G) dst = (__nv_bfloat16*)kv.k_pool + cache_base + (size_t)(head - H) * kv.page_size * d;
-    else dst = (__nv_bfloat16*)kv.v_pool + cache_base + (size_t)(head - H - G) * kv.page_size * d;
-    if (head < H + G) {
-        const float4* cs = reinterpret_cast<const float4*>(table + ((size_t)pos * (d >> 1) + c * 4) * 2);
-        float4 cs0 = cs[0], cs1 = cs[1];                         // (cos, sin) of pairs 0,1 and 2,3
-        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
-        float2 x0 = __bfloat1622float2(p2[0]), x1 = __bfloat1622float2(p2[1]);
-        float2 x2 = __bfloat1622float2(p2[2]), x3 = __bfloat1622float2(p2[3]);
-        p2[0] = __floats2bfloat162_rn(x0.x * cs0.x - x0.y * cs0.y, x0.y * cs0.x + x0.x * cs0.y);
-        p2[1] = __floats2bfloat162_rn(x1.x * cs0.z - x1.y * cs0.w, x1.y * cs0.z + x1.x * cs0.w);
-        p2[2] = __floats2bfloat162_rn(x2.x * cs1.x - x2.y * cs1.y, x2.y * cs1.x + x2.x * cs1.y);
-        p2[3] = __floats2bfloat162_rn(x3.x * cs1.z - x3.y * cs1.w, x3.y * cs1.z + x3.x * cs1.w);
+    const __nv_bfloat16* src = qkv + (size_t)t * (H + 2 * G) * d;
+    const float* cs_row = table + (size_t)pos * (d >> 1) * 2;
+    for (int base = 0; base < n_items; base += ROPE_VEC_ITEMS * blockDim.x) {
+        uint4 raw[ROPE_VEC_ITEMS];
+        float4 cs0[ROPE_VEC_ITEMS], cs1[ROPE_VEC_ITEMS];
+#pragma unroll
+        for (int u = 0; u < ROPE_VEC_ITEMS; u++) {
+            const int item = base + u * blockDim.x + threadIdx.x;
+            if (item < n_items) {
+                raw[u] = *reinterpret_cast<const uint4*>(src + (size_t)item * 8);       // items lie one after the other in qkv
+                const int c = item % d8;
+                const float4* cs = reinterpret_cast<const float4*>(cs_row + c * 8);
+                cs0[u] = cs[0];                                  // (cos, sin) of pairs 0,1 and 2,3
+                cs1[u] = cs[1];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < ROPE_VEC_ITEMS; u++) {
+            const int item = base + u * blockDim.x + threadIdx.x;
+            if (item >= n_items) continue;
+            const int head = item / d8, c = item - head * d8;    // head over q, k, v; c: which 8 elements
+            __nv_bfloat16* dst;
+            if (head < H) dst = q_out + ((size_t)t * H + head) * d;
+            else if (head < H + G) dst = (__nv_bfloat16*)kv.k_pool + cache_base + (size_t)(head - H) * kv.page_size * d;
+            else dst = (__nv_bfloat16*)kv.v_pool + cache_base + (size_t)(head - H - G) * kv.page_size * d;
+            if (head < H + G) {
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw[u]);
+                float2 x0 = __bfloat1622float2(p2[0]), x1 = __bfloat1622float2(p2[1]);
+                float2 x2 = __bfloat1622float2(p2[2]), x3 = __bfloat1622float2(p2[3]);
+                p2[0] = __floats2bfloat162_rn(x0.x * cs0[u].x - x0.y * cs0[u].y, x0.y * cs0[u].x + x0.x * cs0[u].y);
+                p2[1] = __floats2bfloat162_rn(x1.x * cs0[u].z - x1.y * cs0[u].w, x1.y * cs0[u].z + x1.x * cs0[u].w);
+                p2[2] = __floats2bfloat162_rn(x2.x * cs1[u].x - x2.y * cs1[u].y, x2.y * cs1[u].x + x2.x * cs1[u].y);
+                p2[3] = __floats2bfloat162_rn(x3.x * cs1[u].z - x3.y * cs1[u].w, x3.y * cs1[u].z + x3.x * cs1[u].w);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 8) = raw[u];
+        }
     }
-    *reinterpret_cast<uint4*>(dst + c * 8) = raw;
 }
 
 // src: qkv [T, (H+2G)d] of type dt, or, with n_partials > 0, float partial sums [n_partials][T][(H+2G)d].
@@ -394,8 +420,10 @@ GFB_API int gfb_rope_append(const void* src, int n_partials, void* q_out, int dt
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     if (dt == GFB_BF16 && n_partials == 0 && pairing == 0 && d % 8 == 0 && n_tokens >= 64) {
         int vitems = (H + (append ? 2 * G : 0)) * (d / 8);
-        dim3 vgrid(n_tokens, (vitems + 127) / 128);
-        cudaError_t ve = gfb_launch(rope_append_vec_kernel, vgrid, dim3(128), 0, stream, (const __nv_bfloat16*)src,
+        dim3 vgrid(n_tokens);
+        int vthreads = ((vitems + ROPE_VEC_ITEMS - 1) / ROPE_VEC_ITEMS + 31) / 32 * 32;
+        if (vthreads > 256) vthreads = 256;
+        cudaError_t ve = gfb_launch(rope_append_vec_kernel, vgrid, dim3(vthreads), 0, stream, (const __nv_bfloat16*)src,
                                     (__nv_bfloat16*)q_out, kv, b, table, table_len, H, G, d, append, status);
         return gfb_check(ve, "gfb_rope_append (vector)");
     }
