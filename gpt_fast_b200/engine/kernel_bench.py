@@ -111,6 +111,16 @@ def bench_sample(a):
     print(f"argmax batch={a.batch} vocab={a.vocab}: {us:.1f} us")
 
 
+def bench_norm(a):
+    """RMSNorm of the residual stream, as a decode step runs it: the rows' pending partial sums are added on the way."""
+    x = torch.randn(a.rows, a.dim, device="cuda")
+    w = torch.ones(a.dim, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(a.rows, a.dim, device="cuda", dtype=torch.bfloat16)
+    pending = torch.randn(a.partials, a.rows, a.dim, device="cuda") if a.partials else None
+    us = graph_time_us(lambda i: ops.rmsnorm(x, w, 1e-5, out, None, pending), a.reps)
+    print(f"rmsnorm rows={a.rows} dim={a.dim} pending partial sums={a.partials}: {us:.1f} us")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kernel_bench")
     sub = ap.add_subparsers(dest="what", required=True)
@@ -128,8 +138,11 @@ def main(argv=None):
     p = sub.add_parser("sample")
     p.add_argument("--batch", type=int, default=8); p.add_argument("--vocab", type=int, default=128256)
     p.add_argument("--top_k", type=int, default=200); p.add_argument("--reps", type=int, default=10)
+    p = sub.add_parser("norm")
+    p.add_argument("--rows", type=int, default=8); p.add_argument("--dim", type=int, default=4096)
+    p.add_argument("--partials", type=int, default=9); p.add_argument("--reps", type=int, default=10)
     a = ap.parse_args(argv)
-    {"linear": bench_linear, "attention": bench_attention, "sample": bench_sample}[a.what](a)
+    {"linear": bench_linear, "attention": bench_attention, "sample": bench_sample, "norm": bench_norm}[a.what](a)
     ops.check_status(ops.new_status("cuda"))
     return 0
 
