@@ -6,7 +6,7 @@
 // head, slice of the sequence's pages) and serves all query heads of the group
 // from one pass over the keys and values, so each cached byte is read once per
 // group, not once per head.  Pages (64 tokens x head_dim, contiguous per head)
-// are brought to shared memory with cp.async, double buffered.  Scores,
+// are brought to shared memory with cp.async, several pages ahead.  Scores,
 // softmax and the weighted sum are 32-bit.  With more than one slice per
 // sequence the blocks write (max, sum, unnormalised output) to scratch and
 // attn_combine merges the slices in ascending order.
@@ -296,7 +296,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     constexpr int KSTEPS = D / 16, NT = D / 8;
     constexpr int TILE = PAGE * PITCH;           // elements per tile
     extern __shared__ __align__(16) uint8_t smem[];
-    __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1
+    __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1 ... : DECODE_NBUF pairs
     __nv_bfloat16* qs = tiles + 2 * DECODE_NBUF * TILE;        // [8][PITCH]
     gfb_pdl_launch();
     gfb_pdl_wait();
