@@ -7,7 +7,7 @@ runs a packed batch of sequences of unequal lengths against the paged cache
 and computes logits only for the rows that are asked for.  It knows no
 architecture: everything specific came in through the spec.
 """
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 

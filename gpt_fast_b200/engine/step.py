@@ -14,7 +14,7 @@ per step).  `Stepper.decode_batch` prepares the fixed-shape one-token-each
 step whose kernel sequence is captured in a CUDA graph and replayed without
 host work; generation and the benchmark use it.
 """
-from typing import List, Optional, Sequence, Union
+from typing import Sequence, Union
 
 import torch
 

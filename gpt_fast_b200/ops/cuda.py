@@ -1,7 +1,7 @@
 """ctypes bindings of the kernel libraries: host-side checks, kernel choice,
 launch on the current stream."""
 import ctypes
-from ctypes import c_float, c_int, c_long, c_longlong, c_ulonglong, c_void_p
+from ctypes import c_float, c_int, c_long, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch

@@ -16,11 +16,11 @@ import os
 import re
 import zlib
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Tuple
 
 import torch
 
-from .plan import Recipe, Source, WeightPlan
+from .plan import WeightPlan
 
 ROLES = ("matrix", "vector", "table")
 
