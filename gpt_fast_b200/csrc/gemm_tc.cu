@@ -403,6 +403,19 @@ template <int EPI, typename TO>
 __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0, int lane, TO* out, int grow0, int gcol0,
                                             int rows, int N, int ldo) {
     float* mine = stage + lane * PSP;
+    // add-into-residual: the chunk's residual values (32 rows x PCW columns, 8 loads of 16 bytes per lane) are
+    // requested first, so that they travel while the accumulator comes out of tensor memory
+    constexpr int ALPR = PCW / 4, ARPI = 32 / ALPR, ANL = 32 / ARPI;
+    float4 res[ANL];
+    if (EPI == EPI_ADD) {
+        const int sub = lane / ALPR, col = (lane % ALPR) * 4;
+#pragma unroll
+        for (int u = 0; u < ANL; u++) {
+            const int r = ARPI * u + sub;
+            if (r < rows && gcol0 + c0 + col < N)
+                res[u] = *reinterpret_cast<const float4*>((float*)out + (size_t)(grow0 + r) * ldo + gcol0 + c0 + col);
+        }
+    }
 #pragma unroll
     for (int c = 0; c < PCW; c += 16) {
         float v[16];
@@ -413,27 +426,15 @@ __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0
     __syncwarp();
     const int gc = gcol0 + c0;
     if (EPI == EPI_ADD || (EPI == EPI_STORE && sizeof(TO) == 4)) {
-        // PCW/4 lanes x float4 cover a row's columns: RPI rows per instruction, 4 x RPI rows in flight
-        constexpr int LPR = PCW / 4, RPI = 32 / LPR;
-        const int sub = lane / LPR, col = (lane % LPR) * 4;
-#pragma unroll 1
-        for (int rr = 0; rr < rows; rr += 4 * RPI) {
-            float4 res[4];
-            if (EPI == EPI_ADD) {
+        // PCW/4 lanes x float4 cover a row's columns: ARPI rows per instruction
+        const int sub = lane / ALPR, col = (lane % ALPR) * 4;
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    int r = rr + RPI * u + sub;
-                    if (r < rows && gc + col < N) res[u] = *reinterpret_cast<const float4*>((float*)out + (size_t)(grow0 + r) * ldo + gc + col);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                int r = rr + RPI * u + sub;
-                if (r < rows && gc + col < N) {
-                    float4 a = *reinterpret_cast<const float4*>(stage + r * PSP + col);
-                    if (EPI == EPI_ADD) { a.x += res[u].x; a.y += res[u].y; a.z += res[u].z; a.w += res[u].w; }
-                    *reinterpret_cast<float4*>((float*)out + (size_t)(grow0 + r) * ldo + gc + col) = a;
-                }
+        for (int u = 0; u < ANL; u++) {
+            const int r = ARPI * u + sub;
+            if (r < rows && gc + col < N) {
+                float4 a = *reinterpret_cast<const float4*>(stage + r * PSP + col);
+                if (EPI == EPI_ADD) { a.x += res[u].x; a.y += res[u].y; a.z += res[u].z; a.w += res[u].w; }
+                *reinterpret_cast<float4*>((float*)out + (size_t)(grow0 + r) * ldo + gc + col) = a;
             }
         }
     } else if (EPI == EPI_SWIGLU) {
