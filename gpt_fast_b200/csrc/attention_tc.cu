@@ -44,7 +44,7 @@ constexpr uint32_t COL_O = 256;           // output accumulator, 128 columns
 constexpr uint32_t COL_P = 384;           // two probability buffers of 64 columns (bfloat16 pairs)
 
 struct Bars {
-    unsigned long long q_full;
+    unsigned long long q_full, q_empty, o_free;
     unsigned long long k_full[KV_STAGES], k_empty[KV_STAGES];
     unsigned long long v_full[KV_STAGES], v_empty[KV_STAGES];
     unsigned long long s_full[2], s_empty[2];
@@ -245,11 +245,54 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// One (sequence, tile of TQ query tokens, key/value head) unit of work.
+struct TileWork {
+    int seq, tq0, g;
+    int t_first, nq, slot, pos0, last_pos, first_lo, blk0, n_iter, last_page;
+};
+// Work item w of the grid's list (long tiles first: the tile index runs backwards); false: an empty item.
+__device__ __forceinline__ bool tile_work(const GfbBatch& b, int w, int n_x, int G, int TQ, int window, TileWork& t) {
+    const int xi = w / G;
+    t.g = w - xi * G;
+    t.seq = -1;
+    int left = n_x - 1 - xi;
+    for (int i = 0; i < b.n_seqs; i++) {
+        const int qlen = b.cu_seqlens[i + 1] - b.cu_seqlens[i];
+        const int nt = (qlen + TQ - 1) / TQ;
+        if (left < nt) { t.seq = i; t.tq0 = left * TQ; break; }
+        left -= nt;
+    }
+    if (t.seq < 0) return false;
+    t.t_first = b.cu_seqlens[t.seq];
+    const int qlen = b.cu_seqlens[t.seq + 1] - t.t_first;
+    t.nq = min(TQ, qlen - t.tq0);
+    t.slot = b.slots[t.seq];
+    t.pos0 = b.lengths[t.slot] + t.tq0;
+    t.last_pos = t.pos0 + t.nq - 1;
+    t.first_lo = (window > 0 && t.pos0 - window + 1 > 0) ? t.pos0 - window + 1 : 0;
+    t.blk0 = t.first_lo / KEYS;
+    t.n_iter = t.last_pos / KEYS + 1 - t.blk0;                   // key blocks [blk0, blk0 + n_iter)
+    t.last_page = t.last_pos / PAGE;
+    return true;
+}
+
+// The items are sorted by weight (long tiles first), so the blocks take them in a snake: pass 0 hands items
+// 0 .. P-1 to blocks 0 .. P-1, pass 1 hands items P .. 2P-1 to blocks P-1 .. 0, and so on: the block with the
+// heaviest item of one pass gets the lightest of the next.  (Past the end of the list the index only grows.)
+__device__ __forceinline__ int snake_item(int pass, int block, int P) {
+    return pass * P + ((pass & 1) ? P - 1 - block : block);
+}
+
+// Persistent: every block walks over its share of the n_work items (`snake_item`).  Barriers, tensor memory and the
+// pipeline state are set up once; the counters of K/V stages and score buffers run on across items, so the first
+// loads and the first S = Q K^T of the next item are under way while the softmax warps still write the
+// previous item's output.  Two more barriers order the reuse of Q in shared memory (q_empty: the item's last
+// S has read it) and of O in tensor memory (o_free: the softmax warps have read the finished output).
 __global__ void __launch_bounds__(192, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ page_table, int max_pages, int n_pages_pool,
-                       GfbBatch b, int H, int G, float scale_log2e, int window, int* status) {
+                       GfbBatch b, int H, int G, float scale_log2e, int window, int n_x, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -262,22 +305,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rep = H / G;
     const int TQ = ROWS / rep;
-    // which sequence and tile (long tiles first: the index runs backwards)
-    int seq = -1, tq0 = 0;
-    {
-        int left = (int)gridDim.x - 1 - (int)blockIdx.x;
-        for (int i = 0; i < b.n_seqs; i++) {
-            int qlen = b.cu_seqlens[i + 1] - b.cu_seqlens[i];
-            int nt = (qlen + TQ - 1) / TQ;
-            if (left < nt) { seq = i; tq0 = left * TQ; break; }
-            left -= nt;
-        }
-    }
-    if (seq < 0) return;                      // uniform for the block; nothing was set up yet
-    const int g = blockIdx.y;
+    const int n_work = n_x * G;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
+        mbar_init(smem_u32(&bars->q_empty), 1);
+        mbar_init(smem_u32(&bars->o_free), 4);
         for (int s = 0; s < KV_STAGES; s++) {
             mbar_init(smem_u32(&bars->k_full[s]), 1);
             mbar_init(smem_u32(&bars->k_empty[s]), 1);
@@ -305,51 +338,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     gfb_pdl_launch();
     gfb_pdl_wait();
 
-    const int t_first = b.cu_seqlens[seq];
-    const int qlen = b.cu_seqlens[seq + 1] - t_first;
-    const int nq = min(TQ, qlen - tq0);
-    const int slot = b.slots[seq];
-    const int pos0 = b.lengths[slot] + tq0;
-    const int last_pos = pos0 + nq - 1;
-    const int first_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int blk0 = first_lo / KEYS, blk1 = last_pos / KEYS + 1;        // key blocks [blk0, blk1)
-    const int n_iter = blk1 - blk0;
-    const int last_page = last_pos / PAGE;
-    const int* pt = page_table + (size_t)slot * max_pages;
-
     if (warp == 0) {
         if (lane == 0) {
-            // Q: rows ordered (token, head of group); a 3-D box {64 dims, rep heads, TQ tokens} per half
-            mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * 128 * rep * TQ));
-            tma_load_3d(qs, &map_q, 0, g * rep, t_first + tq0, smem_u32(&bars->q_full));
-            tma_load_3d(qs + HALF_BYTES, &map_q, 64, g * rep, t_first + tq0, smem_u32(&bars->q_full));
-            for (int j = 0; j < n_iter; j++) {
-                const int s = j % KV_STAGES;
-                const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-                int pg[2];
+            uint32_t jj = 0, it = 0;                                     // key blocks and items so far
+            bool ok = true;
+            for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
+                TileWork t;
+                if (!tile_work(b, w, n_x, G, TQ, window, t)) continue;
+                const int* pt = page_table + (size_t)t.slot * max_pages;
+                if (it > 0) ok = mbar_wait(smem_u32(&bars->q_empty), (it - 1u) & 1u, abort_flag, status, 11);
+                if (!ok) break;
+                // Q: rows ordered (token, head of group); a 3-D box {64 dims, rep heads, TQ tokens} per half
+                mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * 128 * rep * TQ));
+                tma_load_3d(qs, &map_q, 0, t.g * rep, t.t_first + t.tq0, smem_u32(&bars->q_full));
+                tma_load_3d(qs + HALF_BYTES, &map_q, 64, t.g * rep, t.t_first + t.tq0, smem_u32(&bars->q_full));
+                it++;
+                for (int j = 0; j < t.n_iter; j++, jj++) {
+                    const int s = jj % KV_STAGES;
+                    const uint32_t ph = (jj / KV_STAGES) & 1u;
+                    int pg[2];
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    int pi = (blk0 + j) * 2 + h;
-                    if (pi > last_page) pi = last_page;                 // no such page: any finite data, masked later
-                    int page = pt[pi];
-                    if (page < 0 || page >= n_pages_pool) { gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi); page = 0; }
-                    pg[h] = page;
-                }
-                if (!mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
-                mbar_expect_tx(smem_u32(&bars->k_full[s]), TILE_BYTES);
+                    for (int h = 0; h < 2; h++) {
+                        int pi = (t.blk0 + j) * 2 + h;
+                        if (pi > t.last_page) pi = t.last_page;         // no such page: any finite data, masked later
+                        int page = pt[pi];
+                        if (page < 0 || page >= n_pages_pool) { gfb_report(status, GFB_ERR_PAGE_TABLE, t.slot, pi); page = 0; }
+                        pg[h] = page;
+                    }
+                    if (!mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }
+                    mbar_expect_tx(smem_u32(&bars->k_full[s]), TILE_BYTES);
 #pragma unroll
-                for (int h = 0; h < 2; h++) {                           // page h -> rows 64h .. 64h+63 of both halves
-                    const int row = (pg[h] * G + g) * PAGE;
-                    tma_load_2d(ks + s * TILE_BYTES + h * (PAGE * 128), &map_k, 0, row, smem_u32(&bars->k_full[s]));
-                    tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
-                }
-                if (!mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag, status, 2)) break;
-                mbar_expect_tx(smem_u32(&bars->v_full[s]), TILE_BYTES);
+                    for (int h = 0; h < 2; h++) {                       // page h -> rows 64h .. 64h+63 of both halves
+                        const int row = (pg[h] * G + t.g) * PAGE;
+                        tma_load_2d(ks + s * TILE_BYTES + h * (PAGE * 128), &map_k, 0, row, smem_u32(&bars->k_full[s]));
+                        tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
+                    }
+                    if (!mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag, status, 2)) { ok = false; break; }
+                    mbar_expect_tx(smem_u32(&bars->v_full[s]), TILE_BYTES);
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int row = (pg[h] * G + g) * PAGE;
-                    tma_load_2d(vs + s * TILE_BYTES + h * (PAGE * 128), &map_v, 0, row, smem_u32(&bars->v_full[s]));
-                    tma_load_2d(vs + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_v, 64, row, smem_u32(&bars->v_full[s]));
+                    for (int h = 0; h < 2; h++) {
+                        const int row = (pg[h] * G + t.g) * PAGE;
+                        tma_load_2d(vs + s * TILE_BYTES + h * (PAGE * 128), &map_v, 0, row, smem_u32(&bars->v_full[s]));
+                        tma_load_2d(vs + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_v, 64, row, smem_u32(&bars->v_full[s]));
+                    }
                 }
             }
         }
@@ -357,10 +388,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16(ROWS, KEYS, 0);
             constexpr uint32_t idesc_o = idesc_bf16(ROWS, D, 1);
-            auto issue_s = [&](int j) -> bool {
-                const int s = j % KV_STAGES, sb = j & 1;
-                if (!mbar_wait(smem_u32(&bars->k_full[s]), (uint32_t)(j / KV_STAGES) & 1u, abort_flag, status, 3)) return false;
-                if (!mbar_wait(smem_u32(&bars->s_empty[sb]), ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag, status, 4)) return false;
+            uint32_t jj = 0, it = 0;
+            bool ok = true;
+            auto issue_s = [&](uint32_t u, bool last_of_item) -> bool {   // S of key block number u (running count)
+                const int s = u % KV_STAGES, sb = u & 1u;
+                if (!mbar_wait(smem_u32(&bars->k_full[s]), (u / KV_STAGES) & 1u, abort_flag, status, 3)) return false;
+                if (!mbar_wait(smem_u32(&bars->s_empty[sb]), ((u >> 1) & 1u) ^ 1u, abort_flag, status, 4)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
@@ -370,24 +403,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 umma_commit(smem_u32(&bars->s_full[sb]));
                 umma_commit(smem_u32(&bars->k_empty[s]));
+                if (last_of_item) umma_commit(smem_u32(&bars->q_empty));   // Q may be overwritten once these have run
                 return true;
             };
-            bool ok = mbar_wait(smem_u32(&bars->q_full), 0, abort_flag, status, 5);
-            ok = ok && issue_s(0);
-            for (int j = 0; j < n_iter && ok; j++) {
-                if (j + 1 < n_iter) ok = issue_s(j + 1);
-                if (!ok) break;
-                const int s = j % KV_STAGES;
-                ok = mbar_wait(smem_u32(&bars->v_full[s]), (uint32_t)(j / KV_STAGES) & 1u, abort_flag, status, 6);
-                ok = ok && mbar_wait(smem_u32(&bars->p_ready), (uint32_t)j & 1u, abort_flag, status, 7);
-                if (!ok) break;
-                tc_fence_after();
+            for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
+                TileWork t;
+                if (!tile_work(b, w, n_x, G, TQ, window, t)) continue;
+                ok = mbar_wait(smem_u32(&bars->q_full), it & 1u, abort_flag, status, 5);
+                ok = ok && issue_s(jj, t.n_iter == 1);
+                for (int j = 0; j < t.n_iter && ok; j++, jj++) {
+                    if (j + 1 < t.n_iter) ok = issue_s(jj + 1, j + 2 == t.n_iter);
+                    if (!ok) break;
+                    const int s = jj % KV_STAGES;
+                    ok = mbar_wait(smem_u32(&bars->v_full[s]), (jj / KV_STAGES) & 1u, abort_flag, status, 6);
+                    ok = ok && mbar_wait(smem_u32(&bars->p_ready), jj & 1u, abort_flag, status, 7);
+                    // the first P V of an item overwrites O: the previous item's output must have been read
+                    if (ok && j == 0 && it > 0) ok = mbar_wait(smem_u32(&bars->o_free), (it - 1u) & 1u, abort_flag, status, 12);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++)                           // 16 keys per MMA: 8 columns of P, 2 KB of V
-                    umma_ts(tmem + COL_O, tmem + COL_P + (j & 1) * 64 + kk * 8,
-                            desc_mnmajor(vs + s * TILE_BYTES + kk * 2048), idesc_o, (j | kk) != 0);
-                umma_commit(smem_u32(&bars->pv_done));
-                umma_commit(smem_u32(&bars->v_empty[s]));
+                    for (int kk = 0; kk < 8; kk++)                       // 16 keys per MMA: 8 columns of P, 2 KB of V
+                        umma_ts(tmem + COL_O, tmem + COL_P + (jj & 1u) * 64 + kk * 8,
+                                desc_mnmajor(vs + s * TILE_BYTES + kk * 2048), idesc_o, (j | kk) != 0);
+                    umma_commit(smem_u32(&bars->pv_done));
+                    umma_commit(smem_u32(&bars->v_empty[s]));
+                }
+                it++;
             }
         }
     } else {
@@ -395,96 +436,100 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int r = q * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
         const int tq = r / rep;
-        const bool row_ok = tq < nq;
-        const int row_pos = pos0 + tq;
-        const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
-        float m_run = -INFINITY, l_run = 0.f;
+        uint32_t jj = 0;
         bool ok = true;
-        for (int j = 0; j < n_iter && ok; j++) {
-            const int sb = j & 1;
-            const int key0 = (blk0 + j) * KEYS;
-            ok = mbar_wait(smem_u32(&bars->s_full[sb]), (uint32_t)(j >> 1) & 1u, abort_flag, status, 8);
-            if (!ok) break;
-            tc_fence_after();
-            const bool need_mask = key0 + KEYS - 1 > pos0 || key0 < first_lo || window > 0 || nq * rep < ROWS;
-            // the whole row of this block into registers: one trip to tensor memory
-            float v[4][32];
-            tmem_ld_row128(lane_base + COL_S + sb * 128, v);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[sb]));    // this block of S is consumed (one arrival per warp)
-            if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
-#pragma unroll
-                for (int c = 0; c < 4; c++)
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int kj = key0 + c * 32 + i;
-                        if (!(row_ok && kj <= row_pos && kj >= row_lo)) v[c][i] = -INFINITY;
-                    }
-            }
-            float mx4[4];                                                // four chains instead of one of 128
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                mx4[c] = fmaxf(v[c][0], v[c][1]);
-#pragma unroll
-                for (int i = 2; i < 32; i += 2) mx4[c] = max3(mx4[c], v[c][i], v[c][i + 1]);
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // The running maximum only has to keep the exponentials in range, so it follows the true maximum
-            // lazily: it moves (and O is rescaled) only when the true maximum has grown by more than 2^8 in
-            // the exponent; until then probabilities may reach 256, which bfloat16 and the 32-bit sums hold.
-            // Sum and output use the same reference, so the quotient at the end is exact either way.
-            float m_new = m_run;
-            if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * scale_log2e > 8.f)) m_new = mx;
-            const float corr = (m_run == -INFINITY) ? 0.f : (m_new == m_run ? 1.f : fast_exp2((m_run - m_new) * scale_log2e));
-            const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
-            // probabilities (2^-inf = 0 for masked scores), rounded to bfloat16 into tensor memory
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t pk[16];
-                float rs_odd = 0.f;                                      // rs4[c] and rs_odd: one packed sum
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float t0, t1;
-                    fma2(v[c][i], v[c][i + 1], scale_log2e, mneg, t0, t1);
-                    const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-                    add2(rs4[c], rs_odd, p0, p1);
-                    pk[i >> 1] = pack2(p0, p1);
-                }
-                rs4[c] += rs_odd;
-                tmem_st16(lane_base + COL_P + sb * 64 + c * 16, pk);
-            }
-            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            // O of the earlier blocks follows the new maximum (after the previous P V has landed)
-            if (j > 0) {
-                ok = mbar_wait(smem_u32(&bars->pv_done), (uint32_t)(j - 1) & 1u, abort_flag, status, 9);
+        for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
+            TileWork t;
+            if (!tile_work(b, w, n_x, G, TQ, window, t)) continue;
+            const bool row_ok = tq < t.nq;
+            const int row_pos = t.pos0 + tq;
+            const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+            float m_run = -INFINITY, l_run = 0.f;
+            for (int j = 0; j < t.n_iter && ok; j++, jj++) {
+                const uint32_t sb = jj & 1u;
+                const int key0 = (t.blk0 + j) * KEYS;
+                ok = mbar_wait(smem_u32(&bars->s_full[sb]), (jj >> 1) & 1u, abort_flag, status, 8);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
-                        float o[32];
-                        tmem_ld32(lane_base + COL_O + c * 32, o);
+                const bool need_mask = key0 + KEYS - 1 > t.pos0 || key0 < t.first_lo || window > 0 || t.nq * rep < ROWS;
+                // the whole row of this block into registers: one trip to tensor memory
+                float v[4][32];
+                tmem_ld_row128(lane_base + COL_S + sb * 128, v);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[sb]));    // this block of S is consumed (one arrival per warp)
+                if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
 #pragma unroll
-                        for (int i = 0; i < 32; i++) o[i] *= corr;
-                        tmem_st32(lane_base + COL_O + c * 32, o);
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int kj = key0 + c * 32 + i;
+                            if (!(row_ok && kj <= row_pos && kj >= row_lo)) v[c][i] = -INFINITY;
+                        }
+                }
+                float mx4[4];                                                // four chains instead of one of 128
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    mx4[c] = fmaxf(v[c][0], v[c][1]);
+#pragma unroll
+                    for (int i = 2; i < 32; i += 2) mx4[c] = max3(mx4[c], v[c][i], v[c][i + 1]);
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                // The running maximum only has to keep the exponentials in range, so it follows the true maximum
+                // lazily: it moves (and O is rescaled) only when the true maximum has grown by more than 2^8 in
+                // the exponent; until then probabilities may reach 256, which bfloat16 and the 32-bit sums hold.
+                // Sum and output use the same reference, so the quotient at the end is exact either way.
+                float m_new = m_run;
+                if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * scale_log2e > 8.f)) m_new = mx;
+                const float corr = (m_run == -INFINITY) ? 0.f : (m_new == m_run ? 1.f : fast_exp2((m_run - m_new) * scale_log2e));
+                const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
+                // probabilities (2^-inf = 0 for masked scores), rounded to bfloat16 into tensor memory
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t pk[16];
+                    float rs_odd = 0.f;                                      // rs4[c] and rs_odd: one packed sum
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float t0, t1;
+                        fma2(v[c][i], v[c][i + 1], scale_log2e, mneg, t0, t1);
+                        const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                        add2(rs4[c], rs_odd, p0, p1);
+                        pk[i >> 1] = pack2(p0, p1);
+                    }
+                    rs4[c] += rs_odd;
+                    tmem_st16(lane_base + COL_P + sb * 64 + c * 16, pk);
+                }
+                const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                // O of the earlier blocks follows the new maximum (after the previous P V has landed)
+                if (j > 0) {
+                    ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 1u) & 1u, abort_flag, status, 9);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                        for (int c = 0; c < 4; c++) {
+                            float o[32];
+                            tmem_ld32(lane_base + COL_O + c * 32, o);
+#pragma unroll
+                            for (int i = 0; i < 32; i++) o[i] *= corr;
+                            tmem_st32(lane_base + COL_O + c * 32, o);
+                        }
                     }
                 }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready));
+                l_run = l_run * corr + rs;
+                m_run = m_new;
             }
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready));
-            l_run = l_run * corr + rs;
-            m_run = m_new;
-        }
-        if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&bars->pv_done), (uint32_t)(n_iter - 1) & 1u, abort_flag, status, 10);
-        if (ok) {
+            if (ok) ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 1u) & 1u, abort_flag, status, 10);
+            if (!ok) break;
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            const int head = g * rep + (r - tq * rep);
-            __nv_bfloat16* dst = out + ((size_t)(t_first + tq0 + tq) * H + head) * D;
+            const int head = t.g * rep + (r - tq * rep);
+            __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * D;
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
                 float v[32];
@@ -499,6 +544,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->o_free));         // O may be overwritten by the next item
         }
     }
 
@@ -851,11 +899,11 @@ EncodeTiledFn encode_fn() {
 
 // Causal attention for runs of new tokens on tcgen05; head_dim 128, pages of 64, at most 8 heads per group
 // with 128 % (heads per group) == 0.  tiles: query tiles of 128 rows per block, 1 or 2, or 0 to let the
-// function choose by the amount of work.
+// function choose by the amount of work.  max_blocks: cap of the one-tile kernel's grid (0: one block per SM).
 GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                 int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                 const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
-                                int tiles, int* status, cudaStream_t stream) {
+                                int tiles, int max_blocks, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (page_size != PAGE || d != D) return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim %d", PAGE, D);
     if (G <= 0 || H % G) return gfb_fail("gfb_attn_prefill_tc: %d heads over %d groups", H, G);
@@ -894,9 +942,10 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
     }
     cudaError_t e;
     const long blocks2 = ((long)(n_tokens + 2 * TQ - 1) / (2 * TQ)) * G;
-    if (tiles == 2 || (tiles == 0 && blocks2 >= 2L * sms)) {
-        // enough work for two rounds of blocks of two tiles, which share their K/V loads and keep the tensor
-        // pipe busier; with fewer blocks the finer grain of the one-tile kernel balances the SMs better
+    if (tiles == 2 || (tiles == 0 && blocks2 >= 4L * sms)) {
+        // enough work for several rounds of blocks of two tiles, which share their K/V loads and keep the tensor
+        // pipe busier (measured: from about 6,000 tokens of one sequence on, at 32 heads in 8 groups); with less
+        // work the persistent one-tile kernel balances the SMs better
         size_t smem = 1024 + (size_t)(2 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars2);
         static size_t configured2 = 0;
         if (smem > configured2) {
@@ -915,9 +964,12 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
             if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
             configured = smem;
         }
-        dim3 grid((n_tokens + TQ - 1) / TQ + n_seqs, G);
-        e = gfb_launch(attn_prefill_tc_kernel, grid, dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
+        const int n_x = (n_tokens + TQ - 1) / TQ + n_seqs;           // an upper bound of the tiles; surplus items are empty
+        long blocks = (long)n_x * G;
+        const long cap = max_blocks > 0 ? max_blocks : sms;           // one block per SM walks over the items
+        if (blocks > cap) blocks = cap;
+        e = gfb_launch(attn_prefill_tc_kernel, dim3((unsigned)blocks), dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
     }
     return gfb_check(e, "gfb_attn_prefill_tc");
 }

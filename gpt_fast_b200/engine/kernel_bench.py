@@ -92,7 +92,11 @@ def bench_attention(a):
               f"K/V at {kv_bytes / us / 1e3:.0f} GB/s")
         ops.check_status(meta.status)
         return
-    us = graph_time_us(lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d)), a.reps)
+    if a.new > 1 and a.tiles:
+        run = lambda i: ops.kernels()._attention_bf16(q, kv, meta, out, H, G, d, 1 / math.sqrt(d), None, prefill=True, tiles=a.tiles)
+    else:
+        run = lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d))
+    us = graph_time_us(run, a.reps)
     if a.new == 1:
         print(f"attention decode batch={a.batch} context={a.context}: {us:.1f} us, K/V at {kv_bytes / us / 1e3:.0f} GB/s")
     else:
@@ -132,6 +136,7 @@ def main(argv=None):
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=4000)
     p.add_argument("--new", type=int, default=1); p.add_argument("--heads", type=int, default=32)
     p.add_argument("--kv_heads", type=int, default=8); p.add_argument("--head_dim", type=int, default=128)
+    p.add_argument("--tiles", type=int, default=0, help="prefill, head_dim 128: query tiles per block of the tcgen05 kernel (0: its own choice)")
     p.add_argument("--partials", type=int, default=-1,
                    help="decode only: time the fused rotary + append + attention kernel fed by this many partial sums (0: bfloat16 qkv)")
     p.add_argument("--reps", type=int, default=10)

@@ -249,14 +249,15 @@ class CudaKernels:
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)
 
-    def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None, tiles=0):
+    def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None, tiles=0,
+                        max_blocks=0):
         T = batch.n_tokens
         if prefill is None:
             prefill = splits is None and batch.max_q_len > 1 and head_dim in (64, 128)
         if prefill and head_dim == 128 and (n_head // n_kv) in (1, 2, 4, 8) and self.use_tc_attention:
             self._call("attention_tc", "gfb_attn_prefill_tc", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
                        c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(tiles),
-                       _ptr(batch.status), _stream())
+                       c_int(max_blocks), _ptr(batch.status), _stream())
             return
         if prefill:
             self._call("attention_bf16", "gfb_attn_prefill", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),

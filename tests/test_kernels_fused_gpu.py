@@ -82,17 +82,21 @@ PREFILL_CASES = [  # H, G, d, q_lens, starts
 ]
 
 
-@pytest.mark.parametrize("tiles", [1, 2])
+@pytest.mark.parametrize("tiles", [1, 2, -3])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("H,G,d,q_lens,starts", PREFILL_CASES)
 def test_attention_bf16_prefill(tiles, window, H, G, d, q_lens, starts):
-    """tiles: query tiles per block of the tcgen05 kernel (head_dim 128); the other kernels ignore it."""
+    """tiles: query tiles per block of the tcgen05 kernel (head_dim 128); the other kernels ignore it.  -3: the
+    one-tile kernel on three blocks only, so that every block walks through several tiles in a row."""
+    max_blocks = 3 if tiles < 0 else 0
+    tiles = 1 if tiles < 0 else tiles
     batch, table, n_pages = make_batch(q_lens, starts, 5, 64, 24, seed=3)
     T, dt = batch.n_tokens, torch.bfloat16
     kv = PagedKV(rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5), table, 64)
     q = rnd(T, H, d, dtype=dt, seed=6)
     out, ref = torch.empty(T, H * d, dtype=dt, device=DEV), torch.empty(T, H * d, dtype=dt, device=DEV)
-    ops.kernels()._attention_bf16(q, kv, batch, out, H, G, d, 1 / math.sqrt(d), window, prefill=True, tiles=tiles)
+    ops.kernels()._attention_bf16(q, kv, batch, out, H, G, d, 1 / math.sqrt(d), window, prefill=True, tiles=tiles,
+                                  max_blocks=max_blocks)
     REF.attention(q, kv, batch, ref, H, G, d, 1 / math.sqrt(d), window)
     ops.check_status(batch.status)
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)

@@ -80,10 +80,10 @@ def test_8b_layer_sizes_greedy_tokens_agree_between_precisions(big):
 
 
 def test_long_prompt_and_decoding_behind_it():
-    """A 4,800-token prompt (the prefill attention takes two query tiles per block from about 4,700 tokens on at
-    these head counts, and a decode step behind it cuts the cache into many slices), one layer of 16 heads in
-    8 groups with head_dim 128: the last places of the prompt and four decoded places against the plain
-    implementation, judged like the test above."""
+    """A 4,800-token prompt (every block of the prefill attention walks through several tiles, up to 38 key blocks
+    deep, and a decode step behind it cuts the cache into many slices), one layer of 16 heads in 8 groups with
+    head_dim 128: the last places of the prompt and four decoded places against the plain implementation, judged
+    like the test above."""
     cfg = gf.config_from_name("llama-3.1-8b")
     cfg.update(hidden_size=2048, num_attention_heads=16, num_key_value_heads=8, intermediate_size=1024,
                num_hidden_layers=1, vocab_size=512, max_position_embeddings=8192)
