@@ -93,7 +93,8 @@ def bench_attention(a):
         ops.check_status(meta.status)
         return
     if a.new > 1 and a.tiles:
-        run = lambda i: ops.kernels()._attention_bf16(q, kv, meta, out, H, G, d, 1 / math.sqrt(d), None, prefill=True, tiles=a.tiles)
+        run = lambda i: ops.kernels()._attention_bf16(q, kv, meta, out, H, G, d, 1 / math.sqrt(d), None, prefill=True, tiles=a.tiles,
+                                                      max_blocks=a.max_blocks)
     else:
         run = lambda i: ops.attention(q, kv, meta, out, H, G, d, 1 / math.sqrt(d))
     us = graph_time_us(run, a.reps)
@@ -137,6 +138,7 @@ def main(argv=None):
     p.add_argument("--new", type=int, default=1); p.add_argument("--heads", type=int, default=32)
     p.add_argument("--kv_heads", type=int, default=8); p.add_argument("--head_dim", type=int, default=128)
     p.add_argument("--tiles", type=int, default=0, help="prefill, head_dim 128: query tiles per block of the tcgen05 kernel (0: its own choice)")
+    p.add_argument("--max_blocks", type=int, default=0, help="with --tiles 1: cap of the persistent kernel's grid (0: one block per SM)")
     p.add_argument("--partials", type=int, default=-1,
                    help="decode only: time the fused rotary + append + attention kernel fed by this many partial sums (0: bfloat16 qkv)")
     p.add_argument("--reps", type=int, default=10)
