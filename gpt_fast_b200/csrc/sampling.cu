@@ -189,7 +189,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, i
                       float* __restrict__ noise_out) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    __shared__ unsigned int hist[256];
+    __shared__ unsigned int hist[2][256];                     // two histograms in turn: one cluster barrier per pass
     __shared__ unsigned int total[256];
     __shared__ float sv[32];
     __shared__ int si[32];
@@ -203,6 +203,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, i
     if (seed_dev != nullptr) seed = *seed_dev;
     const int rowi = blockIdx.y;
     const int rank = (int)cluster.block_rank();
+    const int lane = threadIdx.x & 31;
     const float* row = logits + (size_t)rowi * V;
     // element e of this thread: index (e * SAMPLE_CLUSTER + rank) * THREADS + tid  (coalesced per block)
     float x[SAMPLE_REGS];
@@ -217,35 +218,61 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, i
     if (!GREEDY && top_k > 0 && top_k < V) {
         uint32_t prefix = 0, mask = 0;
         int remaining = top_k;
-        for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int i = threadIdx.x; i < 256; i += THREADS) hist[i] = 0;
-            __syncthreads();
+        for (int i = threadIdx.x; i < 256; i += THREADS) hist[0][i] = 0;
+        __syncthreads();
+        int pass = 0;
+        for (int shift = 24; shift >= 0; shift -= 8, pass++) {
+            unsigned int* h = hist[pass & 1];
 #pragma unroll
             for (int e = 0; e < SAMPLE_REGS; e++) {
                 int i = (e * SAMPLE_CLUSTER + rank) * THREADS + threadIdx.x;
-                if (i < V) {
-                    uint32_t k = float_key(x[e]);
-                    if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+                const uint32_t k = float_key(x[e]);
+                const bool in = i < V && (k & mask) == prefix;
+                const uint32_t bin = (k >> shift) & 255u;
+                if (shift == 24) {
+                    // the leading byte (sign and exponent) takes few values: one addition per value and warp
+                    const unsigned int same = __match_any_sync(0xffffffffu, in ? bin : 256u);
+                    if (in && lane == __ffs(same) - 1) atomicAdd(&h[bin], (unsigned int)__popc(same));
+                } else if (in) {
+                    atomicAdd(&h[bin], 1u);
                 }
             }
             cluster.sync();                                   // every block's histogram is complete
+            // the other histogram, for the next pass: the cluster's blocks read it before they came to this barrier
+            for (int i = threadIdx.x; i < 256; i += THREADS) hist[(pass & 1) ^ 1][i] = 0;
             if (threadIdx.x < 256) {
                 unsigned int sum = 0;
-                for (int r = 0; r < SAMPLE_CLUSTER; r++) sum += cluster.map_shared_rank(hist, r)[threadIdx.x];
+#pragma unroll
+                for (int r = 0; r < SAMPLE_CLUSTER; r++) sum += cluster.map_shared_rank(h, r)[threadIdx.x];
                 total[threadIdx.x] = sum;
             }
             __syncthreads();
-            if (threadIdx.x == 0) {
-                int left = remaining, bin = 255;
-                for (; bin > 0; bin--) {
-                    int c = (int)total[bin];
-                    if (c >= left) break;
-                    left -= c;
+            if (threadIdx.x < 32) {
+                // the highest bin b with count(bins >= b) >= remaining: lane l holds bins [8 l, 8 l + 8)
+                unsigned int c[8], mine = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) { c[i] = total[lane * 8 + i]; mine += c[i]; }
+                unsigned int above = mine;                    // inclusive sum over this and the higher lanes
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    unsigned int t = __shfl_down_sync(0xffffffffu, above, o);
+                    if (lane + o < 32) above += t;
                 }
-                sh_prefix = prefix | ((uint32_t)bin << shift);
-                sh_remaining = left;
+                const bool here = above >= (unsigned int)remaining && above - mine < (unsigned int)remaining;
+                const unsigned int who = __ballot_sync(0xffffffffu, here);
+                if (who == 0) {                               // fewer elements than remaining (cannot happen with top_k < V)
+                    if (lane == 0) { sh_prefix = prefix; sh_remaining = remaining; }
+                } else if (here) {
+                    int left = remaining - (int)(above - mine), bin = 7;
+                    for (; bin > 0; bin--) {
+                        if ((int)c[bin] >= left) break;
+                        left -= (int)c[bin];
+                    }
+                    sh_prefix = prefix | ((uint32_t)(lane * 8 + bin) << shift);
+                    sh_remaining = left;
+                }
             }
-            cluster.sync();                                   // all remote reads of `hist` are done before it is cleared
+            __syncthreads();
             prefix = sh_prefix;
             remaining = sh_remaining;
             mask |= 255u << shift;
