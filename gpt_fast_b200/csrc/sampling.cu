@@ -229,13 +229,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, i
                 const uint32_t k = float_key(x[e]);
                 const bool in = i < V && (k & mask) == prefix;
                 const uint32_t bin = (k >> shift) & 255u;
-                if (shift == 24) {
-                    // the leading byte (sign and exponent) takes few values: one addition per value and warp
-                    const unsigned int same = __match_any_sync(0xffffffffu, in ? bin : 256u);
-                    if (in && lane == __ffs(same) - 1) atomicAdd(&h[bin], (unsigned int)__popc(same));
-                } else if (in) {
-                    atomicAdd(&h[bin], 1u);
-                }
+                if (in) atomicAdd(&h[bin], 1u);
             }
             cluster.sync();                                   // every block's histogram is complete
             // the other histogram, for the next pass: the cluster's blocks read it before they came to this barrier
