@@ -481,7 +481,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // Sum and output use the same reference, so the quotient at the end is exact either way.
                 float m_new = m_run;
                 if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * scale_log2e > 8.f)) m_new = mx;
-                const float corr = (m_run == -INFINITY) ? 0.f : (m_new == m_run ? 1.f : fast_exp2((m_run - m_new) * scale_log2e));
+                const float corr = (m_run == -INFINITY || m_new == m_run) ? 1.f : fast_exp2((m_run - m_new) * scale_log2e);   // a row without keys so far has O = 0, l = 0
                 const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
                 // probabilities (2^-inf = 0 for masked scores), rounded to bfloat16 into tensor memory
                 float rs4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -502,19 +502,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
                 // O of the earlier blocks follows the new maximum (after the previous P V has landed)
-                if (j > 0) {
+                // (rarely; the next P V is issued only after this warp's arrival below, so the barrier cannot have gone
+                // on by more than the one phase that is waited for, also when earlier phases were never looked at)
+                if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
                     ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 1u) & 1u, abort_flag, status, 9);
                     if (!ok) break;
                     tc_fence_after();
-                    if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-                        for (int c = 0; c < 4; c++) {
-                            float o[32];
-                            tmem_ld32(lane_base + COL_O + c * 32, o);
+                    for (int c = 0; c < 4; c++) {
+                        float o[32];
+                        tmem_ld32(lane_base + COL_O + c * 32, o);
 #pragma unroll
-                            for (int i = 0; i < 32; i++) o[i] *= corr;
-                            tmem_st32(lane_base + COL_O + c * 32, o);
-                        }
+                        for (int i = 0; i < 32; i++) o[i] *= corr;
+                        tmem_st32(lane_base + COL_O + c * 32, o);
                     }
                 }
                 tmem_wait_st();
@@ -524,6 +524,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 l_run = l_run * corr + rs;
                 m_run = m_new;
             }
+            // all P V of the item: a wait for one phase is only valid once the phase before it is known to be over
+            // (S of the last block implies the P V two blocks back), so the last two are waited for in turn
+            if (ok && t.n_iter >= 2) ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 2u) & 1u, abort_flag, status, 10);
             if (ok) ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 1u) & 1u, abort_flag, status, 10);
             if (!ok) break;
             tc_fence_after();
@@ -802,7 +805,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float m_new = m_run;                                         // lazy reference maximum, as in the one-tile kernel
             if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * scale_log2e > 8.f)) m_new = mx;
-            const float corr = (m_run == -INFINITY) ? 0.f : (m_new == m_run ? 1.f : fast_exp2((m_run - m_new) * scale_log2e));
+            const float corr = (m_run == -INFINITY || m_new == m_run) ? 1.f : fast_exp2((m_run - m_new) * scale_log2e);   // a row without keys so far has O = 0, l = 0
             const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
             // P over the first half of this tile's own scores: all of this row's scores are in registers by now,
             // and a thread only ever touches its own row (lane) of tensor memory
@@ -822,19 +825,19 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 rs4[c] += rs_odd;
                 tmem_st16(lane_base + col_s + c * 16, pk);
             }
-            if (n_done > 0) {                                            // O follows the reference maximum, rarely
+            // O follows the reference maximum, rarely (S of this block was issued behind the tile's previous P V, so
+            // that phase is over and the wait only orders the accesses)
+            if (n_done > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
                 ok = mbar_wait(smem_u32(&bars->pv_done[x]), (n_done - 1u) & 1u, abort_flag, status, 9);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
-                        float o[32];
-                        tmem_ld32(lane_base + col_o + c * 32, o);
+                for (int c = 0; c < 4; c++) {
+                    float o[32];
+                    tmem_ld32(lane_base + col_o + c * 32, o);
 #pragma unroll
-                        for (int i = 0; i < 32; i++) o[i] *= corr;
-                        tmem_st32(lane_base + col_o + c * 32, o);
-                    }
+                    for (int i = 0; i < 32; i++) o[i] *= corr;
+                    tmem_st32(lane_base + col_o + c * 32, o);
                 }
             }
             tmem_wait_st();
