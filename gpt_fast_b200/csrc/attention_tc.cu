@@ -50,6 +50,7 @@ struct Bars {
     unsigned long long s_full[2], s_empty[2];
     unsigned long long p_ready;
     unsigned long long pv_done;
+    unsigned long long o_full;                // the item's last P V has landed (one phase per item)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -323,6 +324,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         mbar_init(smem_u32(&bars->p_ready), 4);
         mbar_init(smem_u32(&bars->pv_done), 1);
+        mbar_init(smem_u32(&bars->o_full), 1);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -427,6 +429,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                 desc_mnmajor(vs + s * TILE_BYTES + kk * 2048), idesc_o, (j | kk) != 0);
                     umma_commit(smem_u32(&bars->pv_done));
                     umma_commit(smem_u32(&bars->v_empty[s]));
+                    if (j + 1 == t.n_iter) umma_commit(smem_u32(&bars->o_full));
                 }
                 it++;
             }
@@ -436,7 +439,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int r = q * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
         const int tq = r / rep;
-        uint32_t jj = 0;
+        uint32_t jj = 0, it = 0;                                       // key blocks and items so far
         bool ok = true;
         for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
             TileWork t;
@@ -524,11 +527,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 l_run = l_run * corr + rs;
                 m_run = m_new;
             }
-            // all P V of the item: a wait for one phase is only valid once the phase before it is known to be over
-            // (S of the last block implies the P V two blocks back), so the last two are waited for in turn
-            if (ok && t.n_iter >= 2) ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 2u) & 1u, abort_flag, status, 10);
-            if (ok) ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 1u) & 1u, abort_flag, status, 10);
+            // All P V of the item have landed: a barrier of its own with one phase per item.  (A parity wait on pv_done
+            // is only valid while that barrier can be neither a phase behind nor a phase ahead of the awaited one; at the
+            // end of an item, with the waits of the earlier blocks left out, it could be either.)
+            if (ok) ok = mbar_wait(smem_u32(&bars->o_full), it & 1u, abort_flag, status, 10);
             if (!ok) break;
+            it++;
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const int head = t.g * rep + (r - tq * rep);
