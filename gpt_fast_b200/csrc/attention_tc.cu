@@ -36,6 +36,7 @@ constexpr int KEYS = 128;                 // keys per iteration (two pages)
 constexpr int HALF_BYTES = 128 * 128;     // 128 rows x 64 elements x 2 bytes: one swizzled half tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;
 constexpr int KV_STAGES = 2;
+static_assert(KV_STAGES == 2, "the one-tile kernel frees K/V stage s by the barriers of score buffer s");
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // tensor-memory columns
@@ -45,14 +46,18 @@ constexpr uint32_t COL_P = 384;           // two probability buffers of 64 colum
 
 struct Bars {
     unsigned long long q_full, q_empty, o_free;
-    unsigned long long k_full[KV_STAGES], k_empty[KV_STAGES];
-    unsigned long long v_full[KV_STAGES], v_empty[KV_STAGES];
+    unsigned long long k_full[KV_STAGES];     // (a K stage is free again when the scores of its block are done: s_full,
+    unsigned long long v_full[KV_STAGES];     //  a V stage when its P V is: pv_done; a commit per barrier costs MMA issue time)
     unsigned long long s_full[2], s_empty[2];
     unsigned long long p_ready;
-    unsigned long long pv_done;
+    unsigned long long pv_done[2];            // P V of the even / odd key blocks has landed
     unsigned long long o_full;                // the item's last P V has landed (one phase per item)
+    unsigned long long xch[4];                // per quarter of the rows: both warps of a row have written their half's maximum
+    unsigned long long fin[4];                // the same for their sums at the end of an item
     uint32_t tmem_base;
     int abort_flag;
+    float mx_half[2][2][ROWS];                // [key block parity][half][row]
+    float l_half[2][2][ROWS];                 // [item parity][half][row]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -289,7 +294,7 @@ __device__ __forceinline__ int snake_item(int pass, int block, int P) {
 // loads and the first S = Q K^T of the next item are under way while the softmax warps still write the
 // previous item's output.  Two more barriers order the reuse of Q in shared memory (q_empty: the item's last
 // S has read it) and of O in tensor memory (o_free: the softmax warps have read the finished output).
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ page_table, int max_pages, int n_pages_pool,
@@ -311,19 +316,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
         mbar_init(smem_u32(&bars->q_empty), 1);
-        mbar_init(smem_u32(&bars->o_free), 4);
+        mbar_init(smem_u32(&bars->o_free), 8);
         for (int s = 0; s < KV_STAGES; s++) {
             mbar_init(smem_u32(&bars->k_full[s]), 1);
-            mbar_init(smem_u32(&bars->k_empty[s]), 1);
             mbar_init(smem_u32(&bars->v_full[s]), 1);
-            mbar_init(smem_u32(&bars->v_empty[s]), 1);
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(smem_u32(&bars->s_full[s]), 1);
-            mbar_init(smem_u32(&bars->s_empty[s]), 4);
+            mbar_init(smem_u32(&bars->s_empty[s]), 8);
         }
-        mbar_init(smem_u32(&bars->p_ready), 4);
-        mbar_init(smem_u32(&bars->pv_done), 1);
+        mbar_init(smem_u32(&bars->p_ready), 8);
+        for (int s = 0; s < 4; s++) {
+            mbar_init(smem_u32(&bars->xch[s]), 2);
+            mbar_init(smem_u32(&bars->fin[s]), 2);
+        }
+        for (int s = 0; s < 2; s++) mbar_init(smem_u32(&bars->pv_done[s]), 1);
         mbar_init(smem_u32(&bars->o_full), 1);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -367,7 +374,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         if (page < 0 || page >= n_pages_pool) { gfb_report(status, GFB_ERR_PAGE_TABLE, t.slot, pi); page = 0; }
                         pg[h] = page;
                     }
-                    if (!mbar_wait(smem_u32(&bars->k_empty[s]), ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&bars->s_full[s]), ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }   // the scores of block jj - 2 are done
                     mbar_expect_tx(smem_u32(&bars->k_full[s]), TILE_BYTES);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {                       // page h -> rows 64h .. 64h+63 of both halves
@@ -375,7 +382,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         tma_load_2d(ks + s * TILE_BYTES + h * (PAGE * 128), &map_k, 0, row, smem_u32(&bars->k_full[s]));
                         tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
                     }
-                    if (!mbar_wait(smem_u32(&bars->v_empty[s]), ph ^ 1u, abort_flag, status, 2)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&bars->pv_done[s]), ph ^ 1u, abort_flag, status, 2)) { ok = false; break; }   // P V of block jj - 2 is done
                     mbar_expect_tx(smem_u32(&bars->v_full[s]), TILE_BYTES);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
@@ -404,7 +411,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             desc_kmajor(ks + s * TILE_BYTES + off) + 2 * (k & 3), idesc_s, k != 0);
                 }
                 umma_commit(smem_u32(&bars->s_full[sb]));
-                umma_commit(smem_u32(&bars->k_empty[s]));
                 if (last_of_item) umma_commit(smem_u32(&bars->q_empty));   // Q may be overwritten once these have run
                 return true;
             };
@@ -427,14 +433,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int kk = 0; kk < 8; kk++)                       // 16 keys per MMA: 8 columns of P, 2 KB of V
                         umma_ts(tmem + COL_O, tmem + COL_P + (jj & 1u) * 64 + kk * 8,
                                 desc_mnmajor(vs + s * TILE_BYTES + kk * 2048), idesc_o, (j | kk) != 0);
-                    umma_commit(smem_u32(&bars->pv_done));
-                    umma_commit(smem_u32(&bars->v_empty[s]));
+                    umma_commit(smem_u32(&bars->pv_done[s]));
                     if (j + 1 == t.n_iter) umma_commit(smem_u32(&bars->o_full));
                 }
                 it++;
             }
         }
     } else {
+        // Eight softmax warps: warps 2..5 take the first 64 keys of every block, warps 6..9 the second 64.  Warp q of
+        // either half holds rows 32 q .. 32 q + 31, one row per thread, so a row is shared by two warps on the same SM
+        // sub-partition: while one waits for a result the other issues.  They agree on the row's maximum through
+        // shared memory once per block and add their sums at the end of an item.
+        const int half = warp >= 6 ? 1 : 0;
         const int q = warp & 3;
         const int r = q * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
@@ -447,37 +457,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool row_ok = tq < t.nq;
             const int row_pos = t.pos0 + tq;
             const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
-            float m_run = -INFINITY, l_run = 0.f;
+            float m_run = -INFINITY, l_run = 0.f;                        // l_run: this warp's half of the row's sum
             for (int j = 0; j < t.n_iter && ok; j++, jj++) {
                 const uint32_t sb = jj & 1u;
-                const int key0 = (t.blk0 + j) * KEYS;
+                const int key0 = (t.blk0 + j) * KEYS + half * 64;        // this warp's first key
                 ok = mbar_wait(smem_u32(&bars->s_full[sb]), (jj >> 1) & 1u, abort_flag, status, 8);
                 if (!ok) break;
                 tc_fence_after();
-                const bool need_mask = key0 + KEYS - 1 > t.pos0 || key0 < t.first_lo || window > 0 || t.nq * rep < ROWS;
-                // the whole row of this block into registers: one trip to tensor memory
-                float v[4][32];
-                tmem_ld_row128(lane_base + COL_S + sb * 128, v);
+                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.first_lo || window > 0 || t.nq * rep < ROWS;
+                // this warp's half of the row into registers
+                uint32_t raw[2][32];
+                tmem_ld32_issue(lane_base + COL_S + sb * 128 + half * 64, raw[0]);
+                tmem_ld32_issue(lane_base + COL_S + sb * 128 + half * 64 + 32, raw[1]);
+                tmem_ld_wait32(raw[0]);
+                tmem_ld_wait32(raw[1]);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[sb]));    // this block of S is consumed (one arrival per warp)
+                if (lane == 0) mbar_arrive(smem_u32(&bars->s_empty[sb]));    // one arrival per warp
+                float v[2][32];
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[c][i] = __uint_as_float(raw[c][i]);
                 if (need_mask) {                                             // only blocks on the diagonal or at the window's edge
 #pragma unroll
-                    for (int c = 0; c < 4; c++)
+                    for (int c = 0; c < 2; c++)
 #pragma unroll
                         for (int i = 0; i < 32; i++) {
                             const int kj = key0 + c * 32 + i;
                             if (!(row_ok && kj <= row_pos && kj >= row_lo)) v[c][i] = -INFINITY;
                         }
                 }
-                float mx4[4];                                                // four chains instead of one of 128
+                float mx4[4];                                                // four chains
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    mx4[c] = fmaxf(v[c][0], v[c][1]);
+                    const float* x = &v[c >> 1][(c & 1) * 16];
+                    mx4[c] = fmaxf(x[0], x[1]);
 #pragma unroll
-                    for (int i = 2; i < 32; i += 2) mx4[c] = max3(mx4[c], v[c][i], v[c][i + 1]);
+                    for (int i = 2; i < 16; i += 2) mx4[c] = max3(mx4[c], x[i], x[i + 1]);
                 }
-                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                // the other half's maximum (buffers by block parity: a warp cannot be two blocks ahead of its partner)
+                bars->mx_half[sb][half][r] = mx;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->xch[q]));
+                ok = mbar_wait(smem_u32(&bars->xch[q]), jj & 1u, abort_flag, status, 13);
+                if (!ok) break;
+                mx = fmaxf(mx, bars->mx_half[sb][half ^ 1][r]);
                 // The running maximum only has to keep the exponentials in range, so it follows the true maximum
                 // lazily: it moves (and O is rescaled) only when the true maximum has grown by more than 2^8 in
                 // the exponent; until then probabilities may reach 256, which bfloat16 and the 32-bit sums hold.
@@ -487,37 +513,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const float corr = (m_run == -INFINITY || m_new == m_run) ? 1.f : fast_exp2((m_run - m_new) * scale_log2e);   // a row without keys so far has O = 0, l = 0
                 const float mneg = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;
                 // probabilities (2^-inf = 0 for masked scores), rounded to bfloat16 into tensor memory
-                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                float rs2[2] = {0.f, 0.f};
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < 2; c++) {
                     uint32_t pk[16];
-                    float rs_odd = 0.f;                                      // rs4[c] and rs_odd: one packed sum
+                    float rs_odd = 0.f;                                      // rs2[c] and rs_odd: one packed sum
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         float t0, t1;
                         fma2(v[c][i], v[c][i + 1], scale_log2e, mneg, t0, t1);
                         const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-                        add2(rs4[c], rs_odd, p0, p1);
+                        add2(rs2[c], rs_odd, p0, p1);
                         pk[i >> 1] = pack2(p0, p1);
                     }
-                    rs4[c] += rs_odd;
-                    tmem_st16(lane_base + COL_P + sb * 64 + c * 16, pk);
+                    rs2[c] += rs_odd;
+                    tmem_st16(lane_base + COL_P + sb * 64 + half * 32 + c * 16, pk);
                 }
-                const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-                // O of the earlier blocks follows the new maximum (after the previous P V has landed)
-                // (rarely; the next P V is issued only after this warp's arrival below, so the barrier cannot have gone
-                // on by more than the one phase that is waited for, also when earlier phases were never looked at)
+                const float rs = rs2[0] + rs2[1];
+                // O of the earlier blocks follows the new maximum, each warp its 64 columns, after the previous P V has
+                // landed.  Rarely, so most phases of that barrier are never looked at; the parity wait is valid all the
+                // same: the phase before the awaited one (P V of block jj - 3) is over, since the scores of this block
+                // were issued behind the P V of block jj - 2, and the phase after it (block jj + 1) cannot have begun,
+                // since that P V is issued behind this block's, which waits for this warp's arrival below.
                 if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-                    ok = mbar_wait(smem_u32(&bars->pv_done), (jj - 1u) & 1u, abort_flag, status, 9);
+                    ok = mbar_wait(smem_u32(&bars->pv_done[(jj - 1u) & 1u]), ((jj - 1u) >> 1) & 1u, abort_flag, status, 9);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
+                    for (int c = 0; c < 2; c++) {
                         float o[32];
-                        tmem_ld32(lane_base + COL_O + c * 32, o);
+                        tmem_ld32(lane_base + COL_O + half * 64 + c * 32, o);
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] *= corr;
-                        tmem_st32(lane_base + COL_O + c * 32, o);
+                        tmem_st32(lane_base + COL_O + half * 64 + c * 32, o);
                     }
                 }
                 tmem_wait_st();
@@ -532,15 +560,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // end of an item, with the waits of the earlier blocks left out, it could be either.)
             if (ok) ok = mbar_wait(smem_u32(&bars->o_full), it & 1u, abort_flag, status, 10);
             if (!ok) break;
-            it++;
             tc_fence_after();
+            // the row's sum: both halves are under the same reference
+            bars->l_half[it & 1u][half][r] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->fin[q]));
+            ok = mbar_wait(smem_u32(&bars->fin[q]), it & 1u, abort_flag, status, 14);
+            if (!ok) break;
+            l_run += bars->l_half[it & 1u][half ^ 1][r];
+            it++;
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const int head = t.g * rep + (r - tq * rep);
-            __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * D;
+            __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * D + half * 64;   // each warp stores its 64 columns
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 float v[32];
-                tmem_ld32(lane_base + COL_O + c * 32, v);               // warp-collective: also for idle rows
+                tmem_ld32(lane_base + COL_O + half * 64 + c * 32, v);   // warp-collective: also for idle rows
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -949,9 +984,9 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
     }
     cudaError_t e;
     const long blocks2 = ((long)(n_tokens + 2 * TQ - 1) / (2 * TQ)) * G;
-    if (tiles == 2 || (tiles == 0 && blocks2 >= 4L * sms)) {
+    if (tiles == 2 || (tiles == 0 && blocks2 >= 6L * sms)) {
         // enough work for several rounds of blocks of two tiles, which share their K/V loads and keep the tensor
-        // pipe busier (measured: from about 6,000 tokens of one sequence on, at 32 heads in 8 groups); with less
+        // pipe busier (measured: from about 7,000 tokens of one sequence on, at 32 heads in 8 groups); with less
         // work the persistent one-tile kernel balances the SMs better
         size_t smem = 1024 + (size_t)(2 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars2);
         static size_t configured2 = 0;
@@ -975,7 +1010,7 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
         long blocks = (long)n_x * G;
         const long cap = max_blocks > 0 ? max_blocks : sms;           // one block per SM walks over the items
         if (blocks > cap) blocks = cap;
-        e = gfb_launch(attn_prefill_tc_kernel, dim3((unsigned)blocks), dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+        e = gfb_launch(attn_prefill_tc_kernel, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
                        page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
     }
     return gfb_check(e, "gfb_attn_prefill_tc");
