@@ -252,6 +252,8 @@ struct RopeSource {
     int table_len;
     int pairing;              // 0: pairs (2i, 2i+1); 1: pairs (i, i + D/2)
     int append;               // 0: the layer reads a cache another layer wrote
+    const int* lengths_early; // optional: the lengths to request the first pages on before the preceding kernel has
+                              // ended (null: the batch's own); they are checked against the batch's own afterwards
 };
 
 // x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
@@ -299,26 +301,36 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1 ... : DECODE_NBUF pairs
     __nv_bfloat16* qs = tiles + 2 * DECODE_NBUF * TILE;        // [8][PITCH]
     gfb_pdl_launch();
-    gfb_pdl_wait();
     const int rep = H / G;
     const int t = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
-    const int s = b.tok_seq[t];
-    const int slot = b.slots[s];
-    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first_page = lo / PAGE, last_page = pos / PAGE;
-    const int n_pages = last_page - first_page + 1;
-    const int per = (n_pages + splits - 1) / splits;
-    const int p0 = first_page + z * per;
-    const int p1 = min(last_page + 1, p0 + per);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = lane >> 2, t4 = lane & 3;     // row (head) and column pair of the mma fragments
-
+    // Before the wait for the preceding kernel: what only depends on earlier steps.  The batch's bookkeeping and the
+    // page table are written by the host before the step; the sequence's length is advanced by the last kernel of the
+    // previous step, which has almost certainly ended, so the pages are requested on the length read now and the
+    // length is read again behind the wait.
+    const int s = b.tok_seq[t];
+    const int slot = b.slots[s];
+    const int q_off = t - b.cu_seqlens[s];
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
+    int pos, lo, first_page, last_page, per, p0, p1;
+    auto plan = [&](int len) {
+        pos = len + q_off;
+        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        first_page = lo / PAGE;
+        last_page = pos / PAGE;
+        const int n_pages = last_page - first_page + 1;
+        per = (n_pages + splits - 1) / splits;
+        p0 = first_page + z * per;
+        p1 = min(last_page + 1, p0 + per);
+    };
+    bool bad_page = false;                       // uniform over the block
+    int bad_index = 0;
     auto issue = [&](int page_index, int buf) {
-        int page = pt[page_index];
+        int page = (page_index >= 0 && page_index < kv.max_pages) ? pt[page_index] : -1;
         if (page < 0 || page >= kv.n_pages) {
-            if (tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, page_index);
+            bad_page = true;                     // reported once the length is certain
+            bad_index = page_index;
             page = 0;
         }
         const __nv_bfloat16* ksrc = (const __nv_bfloat16*)kv.k_pool + ((size_t)page * G + g) * PAGE * D;
@@ -332,11 +344,18 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         }
     };
     // DECODE_NBUF - 1 pages in flight while q is prepared and, later, while a page is worked on
+    auto first_pages = [&]() {
 #pragma unroll
-    for (int a = 0; a < DECODE_NBUF - 1; a++) {
-        if (p0 + a < p1) issue(p0 + a, a);
-        cp_async_commit();
-    }
+        for (int a = 0; a < DECODE_NBUF - 1; a++) {
+            if (p0 + a < p1) issue(p0 + a, a);
+            cp_async_commit();
+        }
+    };
+    const int len_early = __ldcg((rs.lengths_early ? rs.lengths_early : b.lengths) + slot);
+    plan(len_early);
+    first_pages();
+    gfb_pdl_wait();
+    const int len_now = __ldcg(b.lengths + slot);
     // SRC != SRC_Q: the new key and value of this token, kept in registers by the threads that made them.  The
     // slice that owns the last page patches them into its shared-memory copy of that page: the page may have
     // been read before the store to the cache landed.
@@ -344,29 +363,25 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     bool patch = false;
     int off = 0, new_i0 = 0, new_i1 = 1;
     __nv_bfloat16 new0 = __float2bfloat16_rn(0.f), new1 = new0;
+    // the length was another one after all: drop what was requested and start again (uniform over the block)
+    auto settle_length = [&]() {
+        if (len_now != len_early) {
+            cp_async_wait<0>();
+            __syncthreads();
+            bad_page = false;
+            plan(len_now);
+            first_pages();
+        }
+    };
     if (SRC == SRC_Q) {
         for (int i = tid; i < 8 * D; i += THREADS) {
             int row = i / D, col = i - row * D;
             qs[row * PITCH + col] = row < rep ? q[((size_t)t * H + g * rep + row) * D + col] : __float2bfloat16_rn(0.f);
         }
+        settle_length();
     } else {
         constexpr int IT = 8 * half / THREADS;                    // q pairs per thread; one more pair for k or v
         const size_t W = (size_t)(H + 2 * G) * D;
-        const bool ok = pos >= 0 && pos < rs.table_len;
-        if (!ok && tid == 0 && g == 0 && z == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
-        const float* cs_row = rs.table + (size_t)(ok ? pos : 0) * half * 2;
-        const int n_all = last_page - first_page + 1;
-        const int z_last = (n_all - 1) / per;
-        int page = -1;
-        if (rs.append && ok && z == z_last) {
-            off = pos - last_page * PAGE;
-            page = last_page < kv.max_pages ? pt[last_page] : -1;
-            if (page < 0 || page >= kv.n_pages) {
-                if (tid == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
-                page = -1;
-            }
-        }
-        patch = page >= 0 && tid < 2 * half;
         size_t e0[IT + 1], e1[IT + 1];
         int qi0[IT], qi1[IT], qrow[IT], qi[IT];
 #pragma unroll
@@ -382,7 +397,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         }
         const bool is_key = tid < half;
         const int ki = is_key ? tid : tid - half;
-        if (patch) {
+        if (tid < 2 * half) {                                     // the threads that hold a pair of the new key or value
             new_i0 = (is_key && rs.pairing == 1) ? ki : 2 * ki;
             new_i1 = (is_key && rs.pairing == 1) ? ki + half : 2 * ki + 1;
             const size_t e = (size_t)t * W + (size_t)(is_key ? H + g : H + G + g) * D;
@@ -394,6 +409,22 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         }
         float x0[IT + 1], x1[IT + 1];
         load_pairs<SRC, IT + 1>(rs, e0, e1, x0, x1);
+        settle_length();                                           // from here on the position is certain
+        const bool ok = pos >= 0 && pos < rs.table_len;
+        if (!ok && tid == 0 && g == 0 && z == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+        const float* cs_row = rs.table + (size_t)(ok ? pos : 0) * half * 2;
+        const int n_all = last_page - first_page + 1;
+        const int z_last = (n_all - 1) / per;
+        int page = -1;
+        if (rs.append && ok && z == z_last) {
+            off = pos - last_page * PAGE;
+            page = last_page < kv.max_pages ? pt[last_page] : -1;
+            if (page < 0 || page >= kv.n_pages) {
+                if (tid == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
+                page = -1;
+            }
+        }
+        patch = page >= 0 && tid < 2 * half;
 #pragma unroll
         for (int it = 0; it < IT; it++) {
             const float2 cs = *reinterpret_cast<const float2*>(cs_row + 2 * qi[it]);
@@ -501,6 +532,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     }
     cp_async_wait<0>();
     __syncthreads();
+    if (bad_page && tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, bad_index);
 
     // merge the four warps' partial softmaxes; the tile area is free now
     float* Ow = (float*)smem;                                  // [4][8][D]
@@ -856,11 +888,14 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
 // Rotary encoding, cache append and decode attention in one launch (head_dim 64 or 128, bfloat16): `src` is the
 // q/k/v product [T, (H + 2G) d] in bfloat16 (n_part = 0) or its n_part 32-bit partial sums [n_part][T][(H + 2G) d].
 // With append = 0 only q is taken from it (the layer reads a cache that another layer wrote).
+// The kernel asks for its first pages before the preceding kernel has ended, on the lengths as they are then, and
+// reads the lengths again afterwards; lengths_early (optional, per slot like lengths) stands in for the first read,
+// which lets a test make the two differ.
 GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k_pool, void* v_pool, const int* page_table,
                                  int max_pages, int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq,
                                  const int* slots, const int* lengths, int n_seqs, int n_tokens, const float* table,
                                  int table_len, int H, int G, int d, int pairing, int append, float scale, int window,
-                                 int splits, float* scratch, int* status, cudaStream_t stream) {
+                                 int splits, float* scratch, int* status, const int* lengths_early, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (page_size != PAGE) return gfb_fail("gfb_attn_decode_rope: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
     if (d != 64 && d != 128) return gfb_fail("gfb_attn_decode_rope: head_dim %d (64 or 128)", d);
@@ -872,7 +907,7 @@ GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     float* so = scratch;
     float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
-    RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append};
+    RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append, lengths_early};
     cudaError_t e = launch_decode_mma(d, n_part > 0 ? SRC_PARTIALS : SRC_QKV, dim3(n_tokens, G, splits), stream, nullptr, out, so, sml,
                                       kv, b, H, G, scale, window, splits, status, rs);
     if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;

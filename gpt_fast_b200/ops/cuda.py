@@ -276,10 +276,11 @@ class CudaKernels:
                    _ptr(scratch), _ptr(batch.status), _stream())
 
     def rope_append_attention(self, qkv, partials, kv, batch, table, out, n_head, n_kv, head_dim, pairing, append,
-                              scale, window=None) -> bool:
+                              scale, window=None, lengths_early=None) -> bool:
         """Rotary encoding, cache append and attention of a decode step in one launch, where the kernel for
         it fits (bfloat16, one token per sequence, head_dim 64 or 128, pages of 64, at most 8 query heads per
-        key/value head).  Returns False, having done nothing, where it does not."""
+        key/value head).  Returns False, having done nothing, where it does not.  lengths_early (tests only):
+        what the kernel's read of the lengths ahead of its dependency wait is to see."""
         T = batch.n_tokens
         if not (out.dtype == torch.bfloat16 and batch.max_q_len == 1 and head_dim in (64, 128) and kv.page_size == 64
                 and n_head // n_kv <= 8):
@@ -303,7 +304,7 @@ class CudaKernels:
         self._call("attention_bf16", "gfb_attn_decode_rope", _ptr(src), c_int(n_part), _ptr(out), *self._kv_args(kv),
                    *self._batch_args(batch), _ptr(table), c_int(table.shape[0]), c_int(n_head), c_int(n_kv), c_int(head_dim),
                    c_int(_PAIRING[pairing]), c_int(1 if append else 0), c_float(scale), c_int(window or 0), c_int(splits),
-                   _ptr(scratch), _ptr(batch.status), _stream())
+                   _ptr(scratch), _ptr(batch.status), _ptr(lengths_early), _stream())
         return True
 
     # -- sampling --------------------------------------------------------------------------

@@ -183,6 +183,16 @@ def test_rotary_append_and_decode_attention_in_one_kernel(window, pairing, sourc
     torch.testing.assert_close(kv.v_pool.float(), kv_ref.v_pool.float(), rtol=2e-2, atol=2e-2)
     assert not torch.equal(kv.k_pool, k0)                                   # something was appended
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
+    # The kernel asks for its first pages ahead of its dependency wait, on the lengths as they are then, and checks
+    # them afterwards: with other lengths at that first read (one step behind; nonsense) nothing may change.
+    stale = (batch.lengths - 1).clamp(min=0)
+    wild = torch.randint(-5, 1 << 20, batch.lengths.shape, generator=torch.Generator().manual_seed(1)).to(torch.int32).to(DEV)
+    for early in (stale, wild):
+        kv2, out3 = PagedKV(k0.clone(), v0.clone(), table, 64), torch.empty_like(out)
+        assert ops.kernels().rope_append_attention(qkv, partials, kv2, batch, rt, out3, H, G, d, pairing, True, scale, window,
+                                                   lengths_early=early)
+        ops.check_status(batch.status)
+        assert torch.equal(out3, out) and torch.equal(kv2.k_pool, kv.k_pool) and torch.equal(kv2.v_pool, kv.v_pool)
     # append=False: the cache (as the reference left it) is only read
     kept = kv_ref.k_pool.clone()
     out2 = torch.empty_like(out)
