@@ -93,7 +93,6 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
     // just before the first remote write and finds the barrier complete by then
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     gfb_pdl_launch();
-    gfb_pdl_wait();
     const int r = blockIdx.y;
     const int chunk = D / NORM_CLUSTER;
     const int rank = (int)cluster.block_rank();
@@ -101,6 +100,14 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
     const size_t row = (size_t)r * D;
     // the usual case (chunk <= 4 * blockDim): one float4 per thread, kept in registers between the two passes
     const bool in_regs = chunk <= 4 * (int)blockDim.x;
+    // the weights do not depend on the preceding kernel: they are fetched ahead of the wait for it, so that no load
+    // stands between the cluster's sum and the stores
+    float w4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (in_regs && 4 * (int)threadIdx.x < chunk) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) w4[k] = gfb_to_f32(w[c0 + 4 * threadIdx.x + k]);
+    }
+    gfb_pdl_wait();
     float4 keep = make_float4(0.f, 0.f, 0.f, 0.f);
     float ss = 0.f;
     for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
@@ -131,8 +138,21 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
     float total = 0.f;
     for (int k = 0; k < NORM_CLUSTER; k++) total += parts[k];                                  // fixed order
     const float rstd = rsqrtf(total / (float)D + eps);
+    if (in_regs) {
+        const int i = c0 + 4 * threadIdx.x;
+        if (i < c0 + chunk) {
+            // one store of the four results (8 or 16 bytes; rows and chunks are multiples of four elements)
+            struct alignas(4 * sizeof(TO)) Four { TO v[4]; } f;
+            f.v[0] = gfb_from_f32<TO>(keep.x * rstd * w4[0]);
+            f.v[1] = gfb_from_f32<TO>(keep.y * rstd * w4[1]);
+            f.v[2] = gfb_from_f32<TO>(keep.z * rstd * w4[2]);
+            f.v[3] = gfb_from_f32<TO>(keep.w * rstd * w4[3]);
+            *reinterpret_cast<Four*>(out + row + i) = f;
+        }
+        return;
+    }
     for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
-        const float4 v = in_regs ? keep : *reinterpret_cast<const float4*>(x + row + i);
+        const float4 v = *reinterpret_cast<const float4*>(x + row + i);
         TO* o = out + row + i;
         o[0] = gfb_from_f32<TO>(v.x * rstd * gfb_to_f32(w[i]));
         o[1] = gfb_from_f32<TO>(v.y * rstd * gfb_to_f32(w[i + 1]));
