@@ -79,28 +79,30 @@ def test_8b_layer_sizes_greedy_tokens_agree_between_precisions(big):
     assert same >= 1
 
 
-def test_long_prompt_and_decoding_behind_it():
-    """A 4,800-token prompt (every block of the prefill attention walks through several tiles, up to 38 key blocks
-    deep, and a decode step behind it cuts the cache into many slices), one layer of 16 heads in 8 groups with
-    head_dim 128: the last places of the prompt and four decoded places against the plain implementation, judged
-    like the test above."""
+@pytest.mark.parametrize("hidden,heads,n_prompt", [(2048, 16, 4800), (4096, 32, 7296)])
+def test_long_prompt_and_decoding_behind_it(hidden, heads, n_prompt):
+    """A long prompt and four decoded places behind it (the decode step cuts the cache into many slices), one layer
+    with head_dim 128 and 8 key/value heads: the last places of the prompt and the decoded places against the plain
+    implementation, judged like the test above.  4,800 tokens at 16 heads: every block of the one-tile prefill
+    attention kernel walks through several tiles, up to 38 key blocks deep.  7,296 tokens at 32 heads: enough work
+    for the kernel that takes two query tiles per block."""
     cfg = gf.config_from_name("llama-3.1-8b")
-    cfg.update(hidden_size=2048, num_attention_heads=16, num_key_value_heads=8, intermediate_size=1024,
+    cfg.update(hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=8, intermediate_size=1024,
                num_hidden_layers=1, vocab_size=512, max_position_embeddings=8192)
     import tempfile
     with tempfile.TemporaryDirectory() as d:
         gf.write_model_folder(d, cfg, seed=11)
         p, pc = plain_llama.load_folder(d)
-        toks = traces.make_requests(cfg["vocab_size"], [4804], seed=2)["r0"]
+        toks = traces.make_requests(cfg["vocab_size"], [n_prompt + 4], seed=2)["r0"]
         want = plain_llama.forward(toks, p, pc)[-8:]
         noise = plain_llama.forward(toks, p, pc, act=torch.bfloat16)[-8:] - want
         model = gf.load(d, dtype="bfloat16", device="cuda")
         with torch.no_grad():
-            cache = model.new_cache(max_tokens=4864, max_seqs=1)
+            cache = model.new_cache(max_tokens=n_prompt + 64, max_seqs=1)
             st = gf.Stepper(model, cache)
             slot = cache.begin(1)
-            rows = [st.step(slot, [toks[:4800]], [[4796, 4797, 4798, 4799]]).cpu()]
-            for t in toks[4800:]:
+            rows = [st.step(slot, [toks[:n_prompt]], [[n_prompt - 4, n_prompt - 3, n_prompt - 2, n_prompt - 1]]).cpu()]
+            for t in toks[n_prompt:]:
                 rows.append(st.step(slot, [[t]], "last").cpu())
             st.check()
             cache.end(slot)
