@@ -170,10 +170,19 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __rest
                                    const int* __restrict__ rows, int D, float eps) {
     __shared__ float scratch[32];
     gfb_pdl_launch();
-    gfb_pdl_wait();
     const int r = blockIdx.x;
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
     const int nvec = D >> 2;
+    // the weights do not depend on the preceding kernel: fetched ahead of the wait for it, so that no load stands
+    // between the row's sum and the stores
+    float wk[NORM_VEC_MAX][4];
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; k++) {
+        int i = threadIdx.x + k * blockDim.x;
+#pragma unroll
+        for (int e = 0; e < 4; e++) wk[k][e] = i < nvec ? gfb_to_f32(w[4 * i + e]) : 0.f;
+    }
+    gfb_pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
     float4 v[NORM_VEC_MAX];
     float ss = 0.f;
 #pragma unroll
@@ -190,8 +199,8 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __rest
     for (int k = 0; k < NORM_VEC_MAX; k++) {
         int i = threadIdx.x + k * blockDim.x;
         if (i < nvec) {
-            float o0 = v[k].x * rstd * gfb_to_f32(w[4 * i]), o1 = v[k].y * rstd * gfb_to_f32(w[4 * i + 1]);
-            float o2 = v[k].z * rstd * gfb_to_f32(w[4 * i + 2]), o3 = v[k].w * rstd * gfb_to_f32(w[4 * i + 3]);
+            float o0 = v[k].x * rstd * wk[k][0], o1 = v[k].y * rstd * wk[k][1];
+            float o2 = v[k].z * rstd * wk[k][2], o3 = v[k].w * rstd * wk[k][3];
             TO* o = out + (size_t)r * D + 4 * i;
             if (sizeof(TO) == 4) {
                 *reinterpret_cast<float4*>(o) = make_float4(o0, o1, o2, o3);
