@@ -374,15 +374,18 @@ rope_append_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __r
                        GfbPagedKV kv, GfbBatch b, const float* __restrict__ table, int table_len,
                        int H, int G, int d, int append, int* status) {
     gfb_pdl_launch();
-    gfb_pdl_wait();
     // one block per token: the chain token -> sequence -> slot -> position -> page is walked once per block, and a
-    // thread's items (8 elements each, up to ROPE_VEC_ITEMS of them) are loaded together
+    // thread's items (8 elements each, up to ROPE_VEC_ITEMS of them) are loaded together.  The first links of the
+    // chain are the host's bookkeeping of this step and are read ahead of the wait for the preceding kernel; the
+    // lengths are advanced by a kernel (the last one of the previous step) and are read behind it.
     const int t = blockIdx.x;
     const int d8 = d >> 3;
     const int n_items = (H + (append ? 2 * G : 0)) * d8;
     const int s = b.tok_seq[t];
     const int slot = b.slots[s];
-    const int pos = b.lengths[slot] + (t - b.cu_seqlens[s]);
+    const int q_off = t - b.cu_seqlens[s];
+    gfb_pdl_wait();
+    const int pos = b.lengths[slot] + q_off;
     bool ok = pos >= 0 && pos < table_len;
     size_t cache_base = 0;
     if (append) {
