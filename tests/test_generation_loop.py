@@ -1,7 +1,6 @@
 """The generation loop's decisions, on the CPU: how requests are cut into batches,
 when sequences stop, what the callback sees, what goes back to the cache."""
 import pytest
-import torch
 
 import gpt_fast_b200 as gf
 from gpt_fast_b200.engine.generate import _plan_batches, cache_tokens_needed

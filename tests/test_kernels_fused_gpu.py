@@ -7,7 +7,6 @@ import torch
 
 from gpt_fast_b200 import ops
 from gpt_fast_b200.ops.types import PagedKV
-import plain_ops
 from test_kernels_gpu import DEV, REF, make_batch, rnd
 
 pytestmark = pytest.mark.gpu

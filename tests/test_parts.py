@@ -2,8 +2,6 @@
 are registered, built and stepped without a change to the library's files: a
 mixer with state of its own, a mixer that reads a position encoding of another
 kind, and a feed-forward that routes between experts."""
-import math
-
 import pytest
 import torch
 
