@@ -267,6 +267,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         mbar_init(smem_u32(&bars->accum), 1);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // Weights are written by no kernel: the ring is filled with weight tiles at once, before the block's tensor
+        // memory is there and before the wait for the previous kernel (no other thread touches the barriers before
+        // the block's barrier below).
+        const int n_pre = min(stages, nkb);
+        for (int i = 0; i < n_pre; i++) {                   // fresh barriers: every stage is free
+            uint32_t full = smem_u32(&bars->full[i]);
+            mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
+            if (SWAP) tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
+            else tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -286,13 +296,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            const int n_pre = min(stages, nkb);
-            for (int i = 0; i < n_pre; i++) {               // fresh barriers: every stage is free
-                uint32_t full = smem_u32(&bars->full[i]);
-                mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
-                if (SWAP) tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
-                else tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
-            }
+            const int n_pre = min(stages, nkb);             // their weight halves are on their way already
             gfb_pdl_wait();
             for (int i = 0; i < n_pre; i++) {
                 uint32_t full = smem_u32(&bars->full[i]);
