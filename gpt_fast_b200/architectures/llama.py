@@ -19,10 +19,11 @@ def build_spec(a: ModelArgs) -> ModelSpec:
                                  pairing="interleaved"))
     layer = LayerSpec(
         block="prenorm",
-        mixer=PartSpec("attention", dict(dim=a.dim, n_head=a.n_head, n_kv=a.n_local_heads,
-                                         head_dim=a.head_dim, window=None)),
-        feed_forward=PartSpec("swiglu", dict(dim=a.dim, hidden=a.intermediate_size)),
-        mixer_norm=norm, ffn_norm=norm, position=rope,
+        parts=dict(mixer=PartSpec("attention", dict(dim=a.dim, n_head=a.n_head, n_kv=a.n_local_heads,
+                                                    head_dim=a.head_dim, window=None)),
+                   feed_forward=PartSpec("swiglu", dict(dim=a.dim, hidden=a.intermediate_size)),
+                   mixer_norm=norm, ffn_norm=norm),
+        position=rope,
     )
     spec = ModelSpec(
         architecture="llama", dim=a.dim, vocab_size=a.vocab_size,

@@ -21,14 +21,14 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One set of layer parameters.  `block` names the arrangement of the
-    parts (for instance pre-norm residual); each layer picks its own mixer,
-    feed-forward and norms, so layers of one model may differ."""
+    parts (for instance pre-norm residual); `parts` gives one `PartSpec` per
+    role the arrangement declares (`parts.BLOCKS[block].roles`: for 'prenorm'
+    mixer, feed_forward, mixer_norm, ffn_norm), so an arrangement with other
+    roles (one shared norm, post-norms, no feed-forward) needs no change here.
+    Each layer picks its own parts, so layers of one model may differ."""
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
-    position: Optional[PartSpec] = None   # position encoding the mixer applies
+    parts: Dict[str, PartSpec]
+    position: Optional[PartSpec] = None   # position encoding the layer's mixers apply
 
 
 @dataclass(frozen=True)
@@ -55,8 +55,14 @@ class ModelSpec:
     max_position: int = 0                 # longest sequence the model allows
     stop_tokens: tuple = ()               # default stop tokens of generation
     bos_token: Optional[int] = None
+    embed_scale: Optional[float] = None   # factor on the embedding rows; no kernel takes one yet, so only None builds
+    logit_cap: Optional[float] = None     # soft cap on the logits; likewise
 
     def validate(self) -> None:
+        for name in ("embed_scale", "logit_cap"):
+            if getattr(self, name) is not None:
+                raise ValueError(f"ModelSpec.{name} = {getattr(self, name)}: no kernel of this library applies it yet; "
+                                 "refusing rather than ignoring it")
         owners = {}
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):

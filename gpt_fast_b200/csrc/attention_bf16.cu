@@ -351,11 +351,24 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
             cp_async_commit();
         }
     };
-    const int len_early = __ldcg((rs.lengths_early ? rs.lengths_early : b.lengths) + slot);
-    plan(len_early);
-    first_pages();
+    // Only a kernel that appends may ask for pages this early: it patches its own token's row into the copy of the
+    // last page, and all other rows were written in earlier steps.  A kernel that reads what ANOTHER kernel of this
+    // step stores (SRC_Q behind the rotary/append kernel; append == 0 behind the cache entry's owner) must not copy
+    // a page before that store has landed, so it asks behind the wait.
+    const bool early = SRC != SRC_Q && rs.append != 0;        // uniform over the grid
+    int len_early = 0;
+    if (early) {
+        len_early = __ldcg((rs.lengths_early ? rs.lengths_early : b.lengths) + slot);
+        plan(len_early);
+        first_pages();
+    }
     gfb_pdl_wait();
     const int len_now = __ldcg(b.lengths + slot);
+    if (!early) {
+        len_early = len_now;
+        plan(len_now);
+        first_pages();
+    }
     // SRC != SRC_Q: the new key and value of this token, kept in registers by the threads that made them.  The
     // slice that owns the last page patches them into its shared-memory copy of that page: the page may have
     // been read before the store to the cache landed.

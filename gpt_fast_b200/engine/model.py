@@ -16,7 +16,7 @@ from ..cache import Cache, CacheNeeds
 from ..config.spec import ModelSpec, PartSpec
 from ..ops.types import BatchMeta
 from ..parts.residual import Residual
-from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, build_part
+from ..parts import NORMS, POSITIONS, build_block, build_part
 from ..weights.loader import ParamSpec
 
 COMPUTE_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -52,17 +52,7 @@ class Transformer:
             positions.append((ps, obj))
             return obj
 
-        self.blocks = []
-        for ls in spec.layers:
-            pos = position_for(ls.position)
-            mixer = build_part(MIXERS, ls.mixer, dtype=self.dtype, position=pos)
-            ffn = build_part(FEED_FORWARDS, ls.feed_forward, dtype=self.dtype)
-            n1 = build_part(NORMS, ls.mixer_norm, dtype=self.dtype)
-            n2 = build_part(NORMS, ls.ffn_norm, dtype=self.dtype)
-            if ls.block not in BLOCKS:
-                raise KeyError(f"no block arrangement named '{ls.block}'; known: {sorted(BLOCKS)}")
-            self.blocks.append(BLOCKS[ls.block](mixer=mixer, feed_forward=ffn, mixer_norm=n1, ffn_norm=n2,
-                                                dim=spec.dim, dtype=self.dtype))
+        self.blocks = [build_block(ls, spec.dim, self.dtype, position_for(ls.position)) for ls in spec.layers]
         self.positions = [obj for _, obj in positions]
         self.final_norm = build_part(NORMS, spec.final_norm, dtype=self.dtype)
         self.embed_weight = None
@@ -128,7 +118,7 @@ class Transformer:
         needs = {}
         for e in self.spec.schedule:
             if e.owns_cache:
-                needs[e.cache] = self.blocks[e.layer].mixer.cache_needs()
+                needs[e.cache] = self.blocks[e.layer].cache_needs()
         return needs
 
     def new_cache(self, max_tokens: int, max_seqs: Optional[int] = None, max_seq_len: Optional[int] = None,

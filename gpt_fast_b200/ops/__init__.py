@@ -10,6 +10,7 @@ call raises.  `kernels()` returns the object that implements the operations;
 tests may put a stand-in there with `use_kernels` to exercise the host-side
 logic without a GPU.
 """
+from contextlib import contextmanager
 from typing import Optional
 
 import torch
@@ -44,6 +45,26 @@ def use_kernels(obj):
     global _kernels
     prev, _kernels = _kernels, obj
     return prev
+
+
+@contextmanager
+def trace():
+    """Time every kernel launch made inside the block: yields a list that receives (label, start event,
+    stop event) per launch; `trace_times` turns it into milliseconds.  The events sit between the
+    launches, so kernels no longer overlap their neighbours: the times say where a step's work is, not
+    how long the step takes in a CUDA graph.  Not for use under stream capture."""
+    k = kernels()
+    prev, k.trace = k.trace, []
+    try:
+        yield k.trace
+    finally:
+        k.trace = prev
+
+
+def trace_times(records):
+    """[(label, milliseconds)] of a finished trace, in launch order (synchronises)."""
+    torch.cuda.synchronize()
+    return [(label, start.elapsed_time(stop)) for label, start, stop in records]
 
 
 def new_status(device) -> torch.Tensor:

@@ -71,6 +71,8 @@ class CudaKernels:
         self.use_tc_attention = True       # tcgen05 prefill attention where it fits; False: the mma.sync kernel
         self._sm_count = None
         self._status = None
+        self.trace = None                  # a list: (label, start event, stop event) of every launch is appended
+        self._label = None                 # what the next launch is called in the trace (default: the entry point)
 
     def _f(self, lib: str, name: str):
         key = (lib, name)
@@ -85,7 +87,16 @@ class CudaKernels:
 
     def _call(self, lib, name, *args):
         fn = self._f(lib, name)
-        if fn(*args) != 0:
+        trace = self.trace
+        if trace is not None:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        rc = fn(*args)
+        if trace is not None:
+            stop.record()
+            trace.append((self._label or name, start, stop))
+        self._label = None
+        if rc != 0:
             _fail(f"{name}: {fn._lib.gfb_last_error().decode()}")
 
     # -- element-wise / per-row -------------------------------------------------
@@ -177,6 +188,7 @@ class CudaKernels:
             _fail("the residual sum is kept in float32")
         if mode != "add" and out.dtype not in (a.dtype, torch.float32):
             _fail(f"product of {a.dtype} cannot be stored as {out.dtype}")
+        self._label = f"linear {N}x{K} {mode}"
         if a.dtype == torch.bfloat16 and self._tc_fits(M, N, K, mode):
             return self._linear_tc(a, w, out, mode, defer=defer and mode in ("store", "add"))
         if a.dtype == torch.float32 and out.dtype != torch.float32:

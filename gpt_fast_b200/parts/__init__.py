@@ -8,7 +8,7 @@ sees the model's configuration.  Five kinds, one registry each:
     POSITIONS      prepare(max_positions, device); what a mixer needs to place tokens
     MIXERS         cache_needs(); forward(h, batch, view, residual, append)
     FEED_FORWARDS  forward(h, residual)
-    BLOCKS         forward(x32, batch, view, append): the arrangement of the above
+    BLOCKS         roles; cache_needs(); forward(x32, batch, view, append): the arrangement of the above
 
 Every part also has `param_specs()` (name -> weights.loader.ParamSpec) and
 `load(tensors)`.  Mixers and feed-forwards ADD their result into `residual`, the
@@ -28,6 +28,10 @@ MIXERS: Dict[str, Callable] = {}
 FEED_FORWARDS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
 
+# kind of part -> registry; a block arrangement names a kind for each of its roles
+REGISTRIES: Dict[str, Dict[str, Callable]] = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS,
+                                              "feed_forward": FEED_FORWARDS}
+
 
 def _registrar(table: Dict[str, Callable], kind: str):
     def register(name: str, factory: Callable = None):
@@ -46,6 +50,29 @@ register_position = _registrar(POSITIONS, "position encoding")
 register_mixer = _registrar(MIXERS, "mixer")
 register_feed_forward = _registrar(FEED_FORWARDS, "feed-forward")
 register_block = _registrar(BLOCKS, "block")
+
+
+def build_block(layer, dim: int, dtype, position):
+    """Construct the block arrangement a `LayerSpec` names, with one part per declared role."""
+    if layer.block not in BLOCKS:
+        raise KeyError(f"no block arrangement named '{layer.block}'; known: {sorted(BLOCKS)}")
+    cls = BLOCKS[layer.block]
+    roles = dict(cls.roles)
+    optional = set(getattr(cls, "optional_roles", ()))
+    unknown = sorted(set(layer.parts) - set(roles))
+    missing = sorted(set(roles) - set(layer.parts) - optional)
+    if unknown or missing:
+        raise ValueError(f"block '{layer.block}' takes the parts {sorted(roles)}"
+                         + (f"; not given: {missing}" if missing else "") + (f"; not known to it: {unknown}" if unknown else ""))
+    built = {}
+    for role, kind in roles.items():
+        if role not in layer.parts:
+            continue
+        if kind not in REGISTRIES:
+            raise KeyError(f"block '{layer.block}' asks for a part of kind '{kind}'; kinds: {sorted(REGISTRIES)}")
+        extra = {"position": position} if kind == "mixer" else {}
+        built[role] = build_part(REGISTRIES[kind], layer.parts[role], dtype=dtype, **extra)
+    return cls(parts=built, dim=dim, dtype=dtype)
 
 
 def build_part(table: Dict[str, Callable], spec: PartSpec, **extra: Any):

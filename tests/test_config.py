@@ -80,7 +80,7 @@ def test_spec_is_data_and_validates_the_schedule():
     from gpt_fast_b200.config.spec import ModelSpec, ScheduleEntry
     spec = build_spec(ModelArgs.from_json(BASE))
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    assert spec.layers[0].mixer.params["n_kv"] == 2 and spec.layers[0].position.params["scaling"]["factor"] == 8.0
+    assert spec.layers[0].parts["mixer"].params["n_kv"] == 2 and spec.layers[0].position.params["scaling"]["factor"] == 8.0
     bad = ModelSpec("x", 8, 8, spec.layers, [ScheduleEntry(0, 0), ScheduleEntry(1, 0)], spec.final_norm)
     with pytest.raises(ValueError, match="two owners"):
         bad.validate()

@@ -164,8 +164,10 @@ def toy_spec(dim=48, vocab=61):
     norm = PartSpec("rmsnorm", dict(dim=dim, eps=1e-5))
     rope = PartSpec("rope", dict(head_dim=12, base=10000.0))
     ff = PartSpec("swiglu", dict(dim=dim, hidden=80))
-    toy = LayerSpec("prenorm", PartSpec("running_mean", dict(dim=dim, decay=0.5)), ff, norm, norm, None)
-    att = LayerSpec("prenorm", PartSpec("attention", dict(dim=dim, n_head=4, n_kv=2, head_dim=12)), ff, norm, norm, rope)
+    toy = LayerSpec("prenorm", dict(mixer=PartSpec("running_mean", dict(dim=dim, decay=0.5)), feed_forward=ff,
+                                    mixer_norm=norm, ffn_norm=norm))
+    att = LayerSpec("prenorm", dict(mixer=PartSpec("attention", dict(dim=dim, n_head=4, n_kv=2, head_dim=12)), feed_forward=ff,
+                                    mixer_norm=norm, ffn_norm=norm), rope)
     # layer 0 (toy) runs twice with the same weights and a state of its own each time
     return ModelSpec("toy", dim, vocab, [toy, att],
                      [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2)], norm, max_position=256)
@@ -327,10 +329,11 @@ def test_other_toy_parts_position_encoding_and_routed_feed_forward(backend):
     dim, vocab = 40, 53
     norm = PartSpec("rmsnorm", dict(dim=dim, eps=1e-6))
     rope = PartSpec("rope", dict(head_dim=20, base=5000.0))
-    toy = LayerSpec("prenorm", PartSpec("position_bias", dict(dim=dim)), PartSpec("routed", dict(dim=dim, hidden=24, experts=3)),
-                    norm, norm, PartSpec("sinusoid", dict(dim=dim, base=100.0)))
-    att = LayerSpec("prenorm", PartSpec("attention", dict(dim=dim, n_head=2, n_kv=1, head_dim=20)),
-                    PartSpec("swiglu", dict(dim=dim, hidden=56)), norm, norm, rope)
+    toy = LayerSpec("prenorm", dict(mixer=PartSpec("position_bias", dict(dim=dim)),
+                                    feed_forward=PartSpec("routed", dict(dim=dim, hidden=24, experts=3)),
+                                    mixer_norm=norm, ffn_norm=norm), PartSpec("sinusoid", dict(dim=dim, base=100.0)))
+    att = LayerSpec("prenorm", dict(mixer=PartSpec("attention", dict(dim=dim, n_head=2, n_kv=1, head_dim=20)),
+                                    feed_forward=PartSpec("swiglu", dict(dim=dim, hidden=56)), mixer_norm=norm, ffn_norm=norm), rope)
     spec = ModelSpec("toy2", dim, vocab, [toy, att], [ScheduleEntry(0, 0), ScheduleEntry(1, 1)], norm, max_position=128)
     model = Transformer(spec, dtype, device)
     P = {}
