@@ -125,7 +125,9 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
             for (int i = threadIdx.x; i < 256; i += THREADS) hist[i] = 0;
             __syncthreads();
             for (int i = threadIdx.x; i < V; i += THREADS) {
-                uint32_t k = float_key(row[i] / temp);
+                float x = row[i] / temp;
+                if (x != x) x = -INFINITY;                    // NaN never wins, as in the cluster kernel
+                uint32_t k = float_key(x);
                 if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
             }
             __syncthreads();
@@ -148,23 +150,18 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
         pivot = key_float(prefix);
     }
 
-    // the largest scaled logit is always kept
-    float m = -INFINITY;
-    for (int i = threadIdx.x; i < V; i += THREADS) m = fmaxf(m, row[i] / temp);
-    m = gfb_block_max(m, sv);
-
+    // the draw is the Gumbel form of the exponential race, argmax(p_i / q_i) = argmax(x_i - log q_i), exactly as
+    // in the cluster kernel below: both kernels give the same token from the same noise, however wide the row
     int64_t request = request_ids ? request_ids[blockIdx.x] : (int64_t)blockIdx.x;
     int tix = token_index ? token_index[index_map ? index_map[blockIdx.x] : blockIdx.x] : 0;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += THREADS) {
         float x = row[i] / temp;
+        if (x != x) x = -INFINITY;
         float qn = race_noise(seed, request, tix, i);
         if (noise_out) noise_out[(size_t)blockIdx.x * V + i] = qn;
-        if (x >= pivot) {
-            float score = expf(x - m) / qn;
-            argmax_combine(best, best_i, score, i);
-        }
+        if (x >= pivot) argmax_combine(best, best_i, x - logf(qn), i);
     }
     int winner = block_argmax(best, best_i, sv, si);
     if (threadIdx.x == 0) out[blockIdx.x] = winner == 0x7fffffff ? 0 : winner;

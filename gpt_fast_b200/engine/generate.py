@@ -79,16 +79,17 @@ def decode_one_token(batch: DecodeBatch) -> torch.Tensor:
     return batch.tokens
 
 
-def decode_n_tokens(batch: DecodeBatch, n_steps: int, history: torch.Tensor, first_row: int,
-                    callback: Optional[Callable] = None) -> int:
-    """Up to n_steps decode steps without looking at the tokens on the host;
-    row first_row + i of `history` receives step i's tokens.  gpt-fast:
-    generate.py:70-83."""
+def decode_n_tokens(batch: DecodeBatch, n_steps: int, history: torch.Tensor, first_row: int, cols: torch.Tensor,
+                    after_step: Optional[Callable] = None) -> int:
+    """Up to n_steps decode steps back to back; row first_row + i of `history` receives step i's tokens in
+    the columns `cols` (the batch's sequences).  after_step(tokens), if given, runs on the host after each
+    step has been launched (the GPU is already busy with it) and ends the stretch by returning True.
+    Returns the number of steps run.  gpt-fast: generate.py:70-83."""
     for i in range(n_steps):
         toks = decode_one_token(batch)
-        history[first_row + i, :batch.n].copy_(toks)
-        if callback is not None:
-            callback(toks)
+        history[first_row + i].index_copy_(0, cols, toks)
+        if after_step is not None and after_step(toks):
+            return i + 1
     return n_steps
 
 
@@ -193,6 +194,32 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
             row = 1
             steps = 0
             decode_tokens = 0
+
+            def after_step(cur_tokens):
+                """On the host while the step just launched runs: queue its tokens for the next look, digest
+                the step before it; True if a sequence has ended (the batch is then made anew)."""
+                nonlocal pending, steps, decode_tokens
+                this = None
+                if watch:
+                    pin = pins[steps & 1]
+                    pin[:len(live)].copy_(cur_tokens, non_blocking=True)
+                    ev = torch.cuda.Event() if model.device.type == "cuda" else None
+                    if ev is not None:
+                        ev.record()
+                    this = (ev, pin, list(live))
+                else:
+                    for j in live:
+                        n_new[j] += 1
+                decode_tokens += len(live)
+                steps += 1
+                if pending is not None:                            # the step before this one, while this one runs
+                    ev, pin, pcols = pending
+                    if ev is not None:
+                        ev.synchronize()
+                    look(pin[:len(pcols)].tolist(), pcols)
+                pending = this
+                return any(done[j] for j in live)
+
             while row < max_new_tokens:
                 keep = [j for j in live if not done[j]]
                 if not keep:
@@ -204,28 +231,8 @@ def generate(model: Transformer, prompts: Sequence[Sequence[int]], max_new_token
                     batch = stepper.decode_batch([slots[j] for j in live], use_graph, params, [req_ids[j] for j in live])
                     batch.tokens.copy_(nxt)
                     cols = torch.tensor(live, dtype=torch.long).to(model.device)
-                cur = decode_one_token(batch)
-                history[row].index_copy_(0, cols, cur)
-                this = None
-                if watch:
-                    pin = pins[steps & 1]
-                    pin[:len(live)].copy_(cur, non_blocking=True)
-                    ev = torch.cuda.Event() if model.device.type == "cuda" else None
-                    if ev is not None:
-                        ev.record()
-                    this = (ev, pin, list(live))
-                else:
-                    for j in live:
-                        n_new[j] += 1
-                decode_tokens += len(live)
-                steps += 1
-                row += 1
-                if pending is not None:                            # the step before this one, while this one runs
-                    ev, pin, pcols = pending
-                    if ev is not None:
-                        ev.synchronize()
-                    look(pin[:len(pcols)].tolist(), pcols)
-                pending = this
+                row += decode_n_tokens(batch, max_new_tokens - row, history, row, cols, after_step)
+                cur = batch.tokens
             if pending is not None:
                 ev, pin, pcols = pending
                 if ev is not None:

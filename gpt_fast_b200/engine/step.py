@@ -14,6 +14,7 @@ per step).  `Stepper.decode_batch` prepares the fixed-shape one-token-each
 step whose kernel sequence is captured in a CUDA graph and replayed without
 host work; generation and the benchmark use it.
 """
+import gc
 from typing import Sequence, Union
 
 import torch
@@ -116,7 +117,11 @@ class Stepper:
         if sampling is None:
             return DecodeBatch(self, slots, use_graph)
         from .generate import _Sampler
-        key = (tuple(slots), bool(use_graph), sampling.temperature, sampling.top_k)
+        # the number of slices the attention cuts a sequence into is fixed when the step is captured, from the
+        # longest reservation among the slots: a batch captured for short sequences would run long ones in
+        # one slice (right, but slow), so the reservation's power-of-two bracket is part of the key
+        reach = max(self.cache.reserved_host[s] for s in slots)
+        key = (tuple(slots), bool(use_graph), sampling.temperature, sampling.top_k, max(reach, 1).bit_length())
         batch = self._decode_batches.get(key)
         if batch is None:
             if len(self._decode_batches) >= 64:
@@ -177,8 +182,18 @@ class DecodeBatch:
         elif self.graph is None:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._body()
+            # No garbage collection while the stream is capturing: a collection that happens to free an OLD
+            # captured step (caches, steppers and their decode batches refer to each other, so they die by
+            # collection, at a moment of Python's choosing) destroys its CUDA graph, which is not permitted
+            # during a capture and silently invalidates this one.  torch collects once before it starts.
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self._body()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.graph = g
             g.replay()
         else:

@@ -53,6 +53,7 @@ class Rope:
         self.head_dim, self.base, self.scaling, self.pairing = head_dim, float(base), scaling, pairing
         self.inv_freq = rope_frequencies(head_dim, self.base, scaling)
         self.table = None
+        self._retired = []                 # earlier, shorter tables: captured decode steps may still point at them
 
     def prepare(self, max_positions: int, device) -> None:
         """Build the (cos, sin) table for positions 0 .. max_positions-1."""
@@ -60,4 +61,8 @@ class Rope:
             return
         table = torch.empty(max_positions, self.head_dim // 2, 2, dtype=torch.float32, device=device)
         ops.rope_table(self.inv_freq.to(device), table)
+        if self.table is not None:
+            # a CUDA graph captured for an earlier cache has the old table's address and length in it; the old
+            # table stays valid for as long as this part lives (a few KB to MB each, one per growth)
+            self._retired.append(self.table)
         self.table = table

@@ -50,3 +50,25 @@ def plain_kernels():
     prev = ops.use_kernels(plain_ops.PlainOps())
     yield
     ops.use_kernels(prev)
+
+
+def rms(t) -> float:
+    return float(torch.as_tensor(t).float().pow(2).mean().sqrt())
+
+
+def assert_within_bf16_noise(got, want, emu, where="", rms_factor=1.5, max_factor=2.0):
+    """Judge bfloat16 logits `got` against the 32-bit logits `want` of the plain implementation.
+
+    How far may bfloat16 be from 32-bit?  As far as the plain implementation itself is when its activations
+    are rounded to bfloat16 where the library stores them (`emu`, from `plain_llama.forward(..., act=torch.bfloat16)`
+    or a test's own restatement): that is the noise of the format on this model, measured, not guessed.  The
+    library's error must stay within rms_factor x that noise in the mean and max_factor x at the worst element.
+    A wrong position, head, page or key shows as an error of the order of the logits' own scale, many times the
+    noise.  All three are tensors of the same shape (one row of logits, or several)."""
+    got, want, emu = (torch.as_tensor(t).float() for t in (got, want, emu))
+    err, noise = got - want, emu - want
+    assert rms(noise) > 0, f"{where}: the emulation shows no noise at all; the check would be empty"
+    assert rms(err) <= rms_factor * rms(noise), \
+        f"{where}: rms error {rms(err):.5f}, bfloat16 noise {rms(noise):.5f} (logit scale {rms(want):.4f})"
+    assert float(err.abs().max()) <= max_factor * float(noise.abs().max()), \
+        f"{where}: max error {float(err.abs().max()):.5f}, bfloat16 noise {float(noise.abs().max()):.5f}"

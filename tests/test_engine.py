@@ -15,6 +15,7 @@ from gpt_fast_b200.engine.replay import Replayer
 import plain_llama
 import plain_ops
 import traces
+from conftest import assert_within_bf16_noise
 
 LENGTHS = {"tiny-a": [5, 11, 17, 70, 33, 64, 1], "tiny-b": [1, 7, 30, 64, 129, 40, 65]}
 BACKENDS = [
@@ -25,9 +26,10 @@ BACKENDS = [
 
 
 def tolerance(dtype):
-    # float32: rounding of 32-bit sums in another order.  bfloat16: activations are
-    # rounded to 8 bits of mantissa between kernels; logits here are of order 1.
-    return dict(rtol=1e-4, atol=2e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
+    # float32: rounding of 32-bit sums in another order.  bfloat16 is not judged by a tolerance but against
+    # the measured noise of the format on this model (`assert_within_bf16_noise`).
+    assert dtype == "float32"
+    return dict(rtol=1e-4, atol=2e-5)
 
 
 @pytest.fixture(params=BACKENDS)
@@ -59,24 +61,30 @@ def replay(model, steps):
     return outputs
 
 
-def plain_rows(s):
+def plain_rows(s, act=None):
     rows = {}
     for rid, toks in s["reqs"].items():
-        logits = plain_llama.forward(toks, s["p"], s["cfg"])
+        logits = plain_llama.forward(toks, s["p"], s["cfg"], act=act)
         k = traces.tail_of(toks)
         for j in range(len(toks) - k, len(toks)):
             rows[(rid, j)] = logits[j]
     return rows
 
 
-def compare(rows, ref, tol):
+def compare(rows, ref, dtype, emu=None):
+    """float32: close to the plain logits; bfloat16: within the format's noise (`emu`: the plain
+    implementation with activations rounded to bfloat16)."""
     assert set(rows) == set(ref)
     for key in sorted(ref):
         got = torch.as_tensor(rows[key])
-        try:
-            torch.testing.assert_close(got, ref[key], **tol)
-        except AssertionError as e:
-            raise AssertionError(f"first wrong place: request {key[0]}, token {key[1]}\n{e}") from None
+        where = f"first wrong place: request {key[0]}, token {key[1]}"
+        if dtype == "float32":
+            try:
+                torch.testing.assert_close(got, ref[key], **tolerance(dtype))
+            except AssertionError as e:
+                raise AssertionError(f"{where}\n{e}") from None
+        else:
+            assert_within_bf16_noise(got, ref[key], emu[key], where)
 
 
 @pytest.mark.parametrize("cut", ["whole", "stepped", "batched"])
@@ -86,7 +94,7 @@ def test_replay_matches_plain(setup, cut):
         steps = {"whole": traces.whole, "stepped": traces.stepped,
                  "batched": lambda r: traces.batched(r, 3)}[cut](s["reqs"])
         rows = traces.collect(steps, replay(s["model"], steps), s["cfg"]["vocab_size"])
-        compare(rows, plain_rows(s), tolerance(s["dtype"]))
+        compare(rows, plain_rows(s), s["dtype"], plain_rows(s, torch.bfloat16) if s["dtype"] == "bfloat16" else None)
 
 
 def test_cuts_agree_with_each_other(setup):
@@ -98,9 +106,17 @@ def test_cuts_agree_with_each_other(setup):
         for name, fn in (("whole", traces.whole), ("stepped", traces.stepped), ("batched", lambda r: traces.batched(r, 3))):
             steps = fn(s["reqs"])
             got[name] = traces.collect(steps, replay(s["model"], steps), s["cfg"]["vocab_size"])
-        tol = dict(rtol=1e-5, atol=2e-6) if s["dtype"] == "float32" else tolerance("bfloat16")
+        # bfloat16: two ways of running the same tokens are two samples of the format's noise, so they
+        # are compared with each other at twice the single-sample bound
+        emu, ref = (plain_rows(s, torch.bfloat16), plain_rows(s)) if s["dtype"] == "bfloat16" else (None, None)
         for other in ("stepped", "batched"):
-            compare(got[other], {k: torch.as_tensor(v) for k, v in got["whole"].items()}, tol)
+            for key in sorted(got["whole"]):
+                a, b = torch.as_tensor(got[other][key]), torch.as_tensor(got["whole"][key])
+                where = f"{other} against whole: request {key[0]}, token {key[1]}"
+                if s["dtype"] == "float32":
+                    torch.testing.assert_close(a, b, rtol=1e-5, atol=2e-6, msg=lambda m: f"{where}\n{m}")
+                else:
+                    assert_within_bf16_noise(a, b, b + (emu[key] - ref[key]), where, rms_factor=3.0, max_factor=4.0)
 
 
 def test_first_tokens_and_long_decoding(setup):
@@ -118,7 +134,11 @@ def test_first_tokens_and_long_decoding(setup):
         st.check()
         cache.end(slot)
     ref = plain_llama.forward(toks, s["p"], s["cfg"])
+    emu = plain_llama.forward(toks, s["p"], s["cfg"], act=torch.bfloat16) if s["dtype"] == "bfloat16" else None
     for j, row in enumerate(rows):
+        if s["dtype"] == "bfloat16":
+            assert_within_bf16_noise(row, ref[j], emu[j], f"first wrong token: {j}")
+            continue
         try:
             torch.testing.assert_close(row, ref[j], **tolerance(s["dtype"]))
         except AssertionError as e:
@@ -138,9 +158,12 @@ def test_greedy_generation_through_the_entry_point(setup):
         else:
             # bfloat16 may pick another token where two logits are close: follow the engine's
             # own sequence and require that each chosen token is (nearly) the plain argmax
+            # (by how much?  the chosen token's 32-bit logit can trail the best one by at most twice the
+            # largest error of a bfloat16 logit, and that error is bounded by twice the format's measured noise)
             logits = plain_llama.forward(seq[:-1], s["p"], s["cfg"])
+            noise = plain_llama.forward(seq[:-1], s["p"], s["cfg"], act=torch.bfloat16) - logits
             for j in range(len(pr) - 1, len(seq) - 1):
-                assert logits[j, seq[j + 1]] >= logits[j].max() - 6e-2
+                assert logits[j, seq[j + 1]] >= logits[j].max() - 4 * float(noise[j].abs().max()), f"token {j + 1}"
 
 
 def test_sampled_generation_is_the_same_alone_and_in_a_batch(setup):
@@ -153,7 +176,11 @@ def test_sampled_generation_is_the_same_alone_and_in_a_batch(setup):
         if s["dtype"] == "float32":
             assert alone[0] == together[i]
         else:
-            assert alone[0][:len(pr) + 1] == together[i][:len(pr) + 1] or True   # rounding may differ by batch shape
+            # bfloat16 products sum in another order for another batch shape, so a near tie between two noisy
+            # scores may fall the other way and the sequences part there; the noise itself (keyed by seed,
+            # request and place) must be the same, which shows in the first token: its logits come from the
+            # same prompt and the scores of the race are far apart for these seeds
+            assert alone[0][len(pr)] == together[i][len(pr)], f"request {i}: first sampled token differs alone and in a batch"
 
 
 def test_stop_tokens_end_a_sequence_early(setup):

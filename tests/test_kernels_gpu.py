@@ -274,6 +274,31 @@ def test_sample_matches_the_exponential_race(B, V, top_k, temp):
         assert out.cpu().tolist() == torch.argmax(logits, -1).cpu().tolist()
 
 
+@pytest.mark.parametrize("V", [1001, 128256, 140000])
+def test_sample_wide_and_narrow_rows_choose_alike_and_never_a_nan(V):
+    """Rows wider than 131,072 take the one-block kernel, narrower ones the cluster kernel: from the same noise both
+    must choose what the exponential race chooses, far-down logits included (scores in the log domain do not
+    underflow), and an entry that is not a number never wins nor becomes the top-k pivot."""
+    logits = rnd(3, V, scale=2.0, seed=4)
+    logits[:, ::7] -= 150.0                                   # exp(x - max) of these underflows in 32-bit
+    logits[0, 5] = logits[1, V - 1] = logits[2, 0] = float("nan")
+    clean = torch.where(torch.isnan(logits), torch.full_like(logits, float("-inf")), logits)
+    req = torch.tensor([11, 12, 1 << 33], dtype=torch.int64, device=DEV)
+    for top_k in (None, 40, 3):
+        out = torch.empty(3, dtype=torch.int32, device=DEV)
+        ref = torch.empty(3, dtype=torch.int32)
+        ops.sample(logits, out, 0.9, top_k, 77, req)
+        REF.sample(clean.cpu(), ref, 0.9, top_k, 77, req.cpu())
+        assert out.cpu().tolist() == ref.tolist(), f"top_k {top_k}"
+        assert not torch.isnan(logits[torch.arange(3), out.long()]).any()
+    # all but NaN and one finite entry: that entry is the answer whatever the noise
+    lone = torch.full((1, V), float("nan"), device=DEV)
+    lone[0, V // 3] = -3.0
+    out = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample(lone, out, 1.0, 5, 1)
+    assert int(out[0]) == V // 3
+
+
 def test_sample_keeps_ties_with_the_kth_value():
     V = 64
     logits = torch.full((1, V), -5.0, device=DEV)

@@ -9,6 +9,7 @@ import gpt_fast_b200 as gf
 import plain_llama
 import traces
 from gpt_fast_b200.engine.replay import Replayer
+from conftest import assert_within_bf16_noise
 
 pytestmark = pytest.mark.gpu
 
@@ -28,7 +29,7 @@ def big(tmp_path_factory):
             logits = plain_llama.forward(toks, p, pc, act=act)
             for j in range(len(toks) - traces.tail_of(toks), len(toks)):
                 ref[name][(rid, j)] = logits[j]
-    return d, reqs, ref, cfg["vocab_size"]
+    return d, reqs, ref, cfg["vocab_size"], (p, pc)
 
 
 def run(model, steps, V):
@@ -39,7 +40,7 @@ def run(model, steps, V):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_8b_layer_sizes_all_cuts(big, dtype):
-    folder, reqs, refs, V = big
+    folder, reqs, refs, V, _ = big
     ref, emu = refs["float32"], refs["bfloat16"]
     model = gf.load(folder, dtype=dtype, device="cuda")
     with torch.no_grad():
@@ -59,24 +60,27 @@ def test_8b_layer_sizes_all_cuts(big, dtype):
                     # not compared with each other but each with the 32-bit logits: the library's error must
                     # stay within 1.5 x the plain implementation's in the mean and 2 x at the worst element.
                     # A wrong position, head or page shows as an error of the order of the scale itself.
-                    err, noise = got - want, emu[key] - want
-                    rms = lambda t: float(t.pow(2).mean().sqrt())
-                    assert rms(err) <= 1.5 * rms(noise), f"{where}: rms error {rms(err):.4f}, bfloat16 noise {rms(noise):.4f}"
-                    assert float(err.abs().max()) <= 2.0 * float(noise.abs().max()), \
-                        f"{where}: max error {float(err.abs().max()):.4f}, bfloat16 noise {float(noise.abs().max()):.4f}"
+                    assert_within_bf16_noise(got, want, emu[key], where)
 
 
 def test_8b_layer_sizes_greedy_tokens_agree_between_precisions(big):
-    folder, reqs, _, _ = big
+    """Greedy generation in both precisions against the plain implementation: in 32-bit the tokens are the plain
+    argmax wherever its two best logits are not nearly tied; in bfloat16 each chosen token's 32-bit logit trails
+    the best one by no more than the format's measured noise allows (twice the largest error of a logit, which is
+    itself bounded by twice the noise), along the sequence that was actually generated."""
+    folder, reqs, _, _, (p, pc) = big
     prompts = [t[:20] for t in reqs.values() if len(t) >= 20]
-    out = {}
+    n_new = 8
     for dtype in ("float32", "bfloat16"):
         model = gf.load(folder, dtype=dtype, device="cuda")
-        out[dtype], _ = gf.generate(model, prompts, 8, temperature=0.0, stop_tokens=[])
-    same = sum(a == b for a, b in zip(out["float32"], out["bfloat16"]))
-    first = sum(a[20] == b[20] for a, b in zip(out["float32"], out["bfloat16"]))
-    assert first == len(prompts)                     # the first new token agrees; later ones may fork on near-ties
-    assert same >= 1
+        out, _ = gf.generate(model, prompts, n_new, temperature=0.0, stop_tokens=[])
+        for pr, seq in zip(prompts, out):
+            assert seq[:len(pr)] == pr and len(seq) == len(pr) + n_new
+            logits = plain_llama.forward(seq[:-1], p, pc)
+            noise = plain_llama.forward(seq[:-1], p, pc, act=torch.bfloat16) - logits
+            for j in range(len(pr) - 1, len(seq) - 1):
+                margin = 1e-3 if dtype == "float32" else 4 * float(noise[j].abs().max())
+                assert logits[j, seq[j + 1]] >= logits[j].max() - margin, f"{dtype}: new token {j + 1 - len(pr)}"
 
 
 @pytest.mark.parametrize("hidden,heads,n_prompt", [(2048, 16, 4800), (4096, 32, 7296)])
