@@ -299,6 +299,34 @@ def test_sample_wide_and_narrow_rows_choose_alike_and_never_a_nan(V):
     assert int(out[0]) == V // 3
 
 
+@pytest.mark.parametrize("kind", ["five-values", "two-humps", "heavy-tail", "mostly-masked", "constant"])
+def test_sample_on_rows_that_are_far_from_normal(kind):
+    """The sampler looks for the top-k entries above a threshold guessed from the row's mean and deviation; rows
+    whose values are nothing like a normal sample must give the same token as the plain race, by the retries
+    or by the radix select over the whole row."""
+    V, B = 50000, 3
+    g = torch.Generator().manual_seed(5)
+    if kind == "five-values":                             # thousands of ties around the k-th value
+        logits = torch.randint(0, 5, (B, V), generator=g).float()
+    elif kind == "two-humps":
+        logits = torch.randn(B, V, generator=g) + 30.0 * (torch.rand(B, V, generator=g) < 0.001).float()
+    elif kind == "heavy-tail":
+        logits = torch.randn(B, V, generator=g) * torch.exp(2.0 * torch.randn(B, V, generator=g))
+    elif kind == "mostly-masked":                         # fewer finite entries than top_k
+        logits = torch.full((B, V), float("-inf"))
+        logits[:, :37] = torch.randn(B, 37, generator=g)
+    else:
+        logits = torch.full((B, V), 1.25)
+    logits = logits.to(DEV)
+    req = torch.tensor([3, 4, 5], dtype=torch.int64, device=DEV)
+    for top_k in (1, 100, 2000):
+        out = torch.empty(B, dtype=torch.int32, device=DEV)
+        ref = torch.empty(B, dtype=torch.int32)
+        ops.sample(logits, out, 0.7, top_k, 9, req)
+        REF.sample(logits.cpu(), ref, 0.7, top_k, 9, req.cpu())
+        assert out.cpu().tolist() == ref.tolist(), f"{kind}, top_k {top_k}"
+
+
 def test_sample_keeps_ties_with_the_kth_value():
     V = 64
     logits = torch.full((1, V), -5.0, device=DEV)
