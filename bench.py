@@ -216,7 +216,7 @@ def role_of(label, args):
             return "w2_add"
         return "wo_add"
     names = {"gfb_rmsnorm": "rmsnorm", "gfb_attn_decode_rope": "rope_append_attn_decode", "gfb_attn_decode": "attn_decode",
-             "gfb_attn_prefill_tc": "attn_prefill", "gfb_attn_prefill": "attn_prefill", "gfb_rope_append": "rope_append",
+             "gfb_attn_prefill_tc": "attn_prefill", "gfb_rope_append": "rope_append",
              "gfb_sample": "sample", "gfb_embed": "embed", "gfb_advance_lengths": "advance_lengths",
              "gfb_add_partials": "add_partials"}
     return names.get(label, label)

@@ -30,12 +30,6 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-// 2^x by the special-function unit (one instruction; exact enough for probabilities that are rounded to bfloat16)
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -584,211 +578,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     }
 }
 
-// ---- prefill: many new tokens per sequence ------------------------------------------------
-// Causal attention of a run of new tokens over the cache (which already holds their own keys
-// and values).  A block owns one key/value head and a tile of TQ consecutive query tokens of one
-// sequence; its 128 rows are the (token, head of the group) pairs, so the heads of a group share
-// every page that is loaded.  Per page: S = Q K^T and O += P V as mma.sync m16n8k16 with 32-bit
-// accumulation, online softmax in 32-bit registers (two rows per thread), P rounded to bf16 as
-// the A operand of the second product straight from the accumulator registers of the first.
-// Pages wholly above the diagonal are never visited.
-__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-constexpr int PREFILL_THREADS = 256;     // 8 warps x 16 rows
-constexpr int PREFILL_ROWS = 128;
-
-template <int D>
-__global__ void __launch_bounds__(PREFILL_THREADS, 1)
-attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
-                        GfbPagedKV kv, GfbBatch b, int H, int G, float scale_log2e, int window, int* status) {
-    constexpr int PITCH = D + 8;
-    constexpr int KSTEPS = D / 16, NT = D / 8;
-    constexpr int TILE = PAGE * PITCH;
-    extern __shared__ __align__(16) uint8_t smem[];
-    __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1
-    gfb_pdl_launch();
-    gfb_pdl_wait();
-    const int rep = H / G;
-    const int TQ = PREFILL_ROWS / rep;                         // query tokens per block
-    // which sequence and which of its tiles is this block?
-    // Later tiles of a sequence see more keys; blocks are handed out in order of their index, so the
-    // index runs backwards over the tiles and the long ones start first.
-    int seq = -1, tq0 = 0;
-    {
-        int left = (int)gridDim.x - 1 - (int)blockIdx.x;
-        for (int i = 0; i < b.n_seqs; i++) {
-            int qlen = b.cu_seqlens[i + 1] - b.cu_seqlens[i];
-            int nt = (qlen + TQ - 1) / TQ;
-            if (left < nt) { seq = i; tq0 = left * TQ; break; }
-            left -= nt;
-        }
-    }
-    if (seq < 0) return;                                       // the grid is an upper bound
-    const int g = blockIdx.y;
-    const int t_first = b.cu_seqlens[seq];
-    const int qlen = b.cu_seqlens[seq + 1] - t_first;
-    const int nq = min(TQ, qlen - tq0);                        // tokens of this tile
-    const int slot = b.slots[seq];
-    const int pos0 = b.lengths[slot] + tq0;                    // position of the tile's first token
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int gq = lane >> 2, t4 = lane & 3;
-    const int mid = lane >> 3, mr = lane & 7;
-
-    // this thread's two rows
-    int row_tok[2], row_head[2], row_pos[2], row_lo[2];
-    bool row_ok[2];
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        int r = warp * 16 + gq + 8 * i;
-        int tq = r / rep;
-        row_ok[i] = tq < nq;
-        row_tok[i] = t_first + tq0 + tq;
-        row_head[i] = g * rep + (r - tq * rep);
-        row_pos[i] = pos0 + tq;
-        row_lo[i] = (window > 0 && row_pos[i] - window + 1 > 0) ? row_pos[i] - window + 1 : 0;
-    }
-    uint32_t qa[KSTEPS][4];
-#pragma unroll
-    for (int k = 0; k < KSTEPS; k++)
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const __nv_bfloat16* src = q + ((size_t)row_tok[i] * H + row_head[i]) * D + k * 16 + 2 * t4;
-            qa[k][i] = row_ok[i] ? *reinterpret_cast<const uint32_t*>(src) : 0u;          // a0 / a1: dims 2t..
-            qa[k][i + 2] = row_ok[i] ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;  // a2 / a3: dims 8+2t..
-        }
-
-    const int last_pos = pos0 + nq - 1;
-    const int first_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int p0 = first_lo / PAGE, p1 = last_pos / PAGE + 1;
-    const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
-    auto issue = [&](int page_index, int buf) {
-        int page = pt[page_index];
-        if (page < 0 || page >= kv.n_pages) {
-            if (tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, page_index);
-            page = 0;
-        }
-        const __nv_bfloat16* ksrc = (const __nv_bfloat16*)kv.k_pool + ((size_t)page * G + g) * PAGE * D;
-        const __nv_bfloat16* vsrc = (const __nv_bfloat16*)kv.v_pool + ((size_t)page * G + g) * PAGE * D;
-        __nv_bfloat16* kd = tiles + (2 * buf) * TILE;
-        __nv_bfloat16* vd = tiles + (2 * buf + 1) * TILE;
-        for (int c = tid; c < PAGE * (D / 8); c += PREFILL_THREADS) {
-            int row = c / (D / 8), cc = c - row * (D / 8);
-            cp_async16(kd + row * PITCH + cc * 8, ksrc + row * D + cc * 8);
-            cp_async16(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8);
-        }
-    };
-    issue(p0, 0);
-    cp_async_commit();
-
-    float o[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-
-    for (int p = p0; p < p1; p++) {
-        const int buf = (p - p0) & 1;
-        if (p + 1 < p1) issue(p + 1, buf ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf) * TILE);
-        const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf + 1) * TILE);
-
-        float sc[8][4];
-#pragma unroll
-        for (int n = 0; n < 8; n++) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
-#pragma unroll
-        for (int k = 0; k < KSTEPS; k++) {
-#pragma unroll
-            for (int n = 0; n < 8; n += 2) {
-                uint32_t addr = kbase + (uint32_t)((((n + (mid >> 1)) * 8 + mr) * PITCH + k * 16 + (mid & 1) * 8) * 2);
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4(addr, b0, b1, b2, b3);
-                mma_16816(sc[n], qa[k], b0, b1);
-                mma_16816(sc[n + 1], qa[k], b2, b3);
-            }
-        }
-        // online softmax (row i of this thread: accumulator elements 2i, 2i+1).  Scores stay unscaled;
-        // the scale goes into the exponent: p = exp2(s * c - m * c).  Only pages that touch the
-        // diagonal, the window's edge or idle rows need the mask.
-        const bool need_mask = (p + 1) * PAGE - 1 > pos0 || window > 0 || nq * rep < PREFILL_ROWS;
-        if (need_mask) {
-#pragma unroll
-            for (int n = 0; n < 8; n++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int i = e >> 1;
-                    const int j = p * PAGE + n * 8 + 2 * t4 + (e & 1);
-                    if (!(row_ok[i] && j <= row_pos[i] && j >= row_lo[i])) sc[n][e] = -INFINITY;
-                }
-        }
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int n = 0; n < 8; n++) {
-            mx[0] = fmaxf(mx[0], fmaxf(sc[n][0], sc[n][1]));
-            mx[1] = fmaxf(mx[1], fmaxf(sc[n][2], sc[n][3]));
-        }
-        float corr[2], mneg[2];
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-            float m_new = fmaxf(m_run[i], mx[i]);                 // in units of the raw score
-            corr[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f((m_run[i] - m_new) * scale_log2e);
-            m_run[i] = m_new;
-            mneg[i] = (m_new == -INFINITY) ? 0.f : -m_new * scale_log2e;   // all masked so far: exp2(-inf) = 0 anyway
-        }
-        float rs[2] = {0.f, 0.f};
-#pragma unroll
-        for (int n = 0; n < 8; n++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int i = e >> 1;
-                float pe = fast_exp2(fmaf(sc[n][e], scale_log2e, mneg[i]));   // 2^-inf = 0 for masked scores
-                sc[n][e] = pe;
-                rs[i] += pe;
-            }
-#pragma unroll
-        for (int i = 0; i < 2; i++) l_run[i] = l_run[i] * corr[i] + rs[i];     // per-thread partial; the four lanes of a row are summed at the end
-#pragma unroll
-        for (int j = 0; j < NT; j++) { o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1]; }
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++) {                       // 16 keys per step
-            uint32_t pa[4];
-            pa[0] = pack2(sc[2 * kk][0], sc[2 * kk][1]);
-            pa[1] = pack2(sc[2 * kk][2], sc[2 * kk][3]);
-            pa[2] = pack2(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-            pa[3] = pack2(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
-#pragma unroll
-            for (int j = 0; j < NT; j += 2) {
-                uint32_t addr = vbase + (uint32_t)(((kk * 16 + (mid & 1) * 8 + mr) * PITCH + (j + (mid >> 1)) * 8) * 2);
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(addr, b0, b1, b2, b3);
-                mma_16816(o[j], pa, b0, b1);
-                mma_16816(o[j + 1], pa, b2, b3);
-            }
-        }
-        __syncthreads();
-    }
-    cp_async_wait<0>();
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        float l = l_run[i];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        if (!row_ok[i]) continue;
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = out + ((size_t)row_tok[i] * H + row_head[i]) * D + 2 * t4;
-#pragma unroll
-        for (int j = 0; j < NT; j++)
-            *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
-    }
-}
-
 __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
                                     __nv_bfloat16* __restrict__ out, int H, int d, int splits) {
     gfb_pdl_launch();
@@ -973,31 +762,4 @@ GFB_API int gfb_attn_decode_noalloc(const void* q, void* out, void* k_pool, void
     }
     return gfb_attn_decode(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
                            lengths, n_seqs, n_tokens, H, G, d, scale, window, splits, scratch, status, stream);
-}
-
-
-// Causal attention for runs of new tokens (prefill); head_dim 64 or 128, at most 8 heads per group.
-GFB_API int gfb_attn_prefill(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
-                             int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
-                             const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
-                             int* status, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (page_size != PAGE) return gfb_fail("gfb_attn_prefill: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
-    if (d != 64 && d != 128) return gfb_fail("gfb_attn_prefill: head_dim %d (the kernel is built for 64 and 128)", d);
-    if (G <= 0 || H % G || H / G > MAX_REP) return gfb_fail("gfb_attn_prefill: %d heads over %d groups (at most %d per group)", H, G, MAX_REP);
-    const int rep = H / G, TQ = PREFILL_ROWS / rep;
-    GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
-    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
-    dim3 grid((n_tokens + TQ - 1) / TQ + n_seqs, G);          // upper bound on the number of tiles
-    size_t smem = (size_t)4 * PAGE * (d + 8) * 2;
-    auto kern = d == 128 ? attn_prefill_mma_kernel<128> : attn_prefill_mma_kernel<64>;
-    static size_t conf[2] = {0, 0};
-    if (smem > 48 * 1024 && smem > conf[d == 128]) {
-        cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
-        conf[d == 128] = smem;
-    }
-    cudaError_t e = gfb_launch(kern, grid, dim3(PREFILL_THREADS), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b,
-                               H, G, scale * 1.4426950408889634f, window, status);
-    return gfb_check(e, "gfb_attn_prefill");
 }

@@ -1,9 +1,10 @@
-// Prefill attention on the 5th-generation tensor cores (tcgen05), head_dim 128, bfloat16.
+// Prefill attention on the 5th-generation tensor cores (tcgen05), head_dim 128 or 64, bfloat16.
 //
 // Causal attention of a run of new tokens over the paged cache (gpt-fast: the
 // SDPA call of model.py:209-211).  A block owns one key/value head and a tile of
-// TQ = 128 / (heads per group) consecutive query tokens of one sequence; its 128
-// rows are the (token, head of the group) pairs, one per tensor-memory lane.
+// TQ = 128 / (heads per group) consecutive query tokens of one sequence (rounded down: 42 tokens
+// and 126 rows for 3 heads per group); its rows are the (token, head of the group) pairs, one per
+// tensor-memory lane.
 // Keys and values are visited 128 at a time (two pages of 64):
 //
 //   S = Q K^T        tcgen05.mma, A = Q and B = K from shared memory (TMA, 128B swizzle),
@@ -299,6 +300,7 @@ __device__ __forceinline__ int snake_item(int pass, int block, int P) {
 // loads and the first S = Q K^T of the next item are under way while the softmax warps still write the
 // previous item's output.  Two more barriers order the reuse of Q in shared memory (q_empty: the item's last
 // S has read it) and of O in tensor memory (o_free: the softmax warps have read the finished output).
+template <int DH>
 __global__ void __launch_bounds__(320, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -318,7 +320,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int rep = H / G;
     const int TQ = ROWS / rep;
     const int n_work = n_x * G;
+    constexpr int NH = DH / 64;                                          // swizzled half tiles (64 dims) per operand tile
 
+    // Rows beyond TQ * rep (heads per group that do not divide 128: 126 rows for 3, 125 for 5, ...) are never
+    // written by the Q copy; they are zeroed once so that their scores are finite.  Nothing of them is stored.
+    for (int i = threadIdx.x; i < (ROWS - TQ * rep) * 8 * NH; i += blockDim.x) {
+        const int row = TQ * rep + i / (8 * NH), chunk = i % (8 * NH);  // NH halves x 8 chunks of 16 bytes per row
+        *reinterpret_cast<uint4*>(aligned + (chunk >> 3) * HALF_BYTES + row * 128 + (chunk & 7) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
         mbar_init(smem_u32(&bars->q_empty), 1);
@@ -364,9 +374,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (it > 0) ok = mbar_wait(smem_u32(&bars->q_empty), (it - 1u) & 1u, abort_flag, status, 11);
                 if (!ok) break;
                 // Q: rows ordered (token, head of group); a 3-D box {64 dims, rep heads, TQ tokens} per half
-                mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * 128 * rep * TQ));
+                mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(NH * 128 * rep * TQ));
                 tma_load_3d(qs, &map_q, 0, t.g * rep, t.t_first + t.tq0, smem_u32(&bars->q_full));
-                tma_load_3d(qs + HALF_BYTES, &map_q, 64, t.g * rep, t.t_first + t.tq0, smem_u32(&bars->q_full));
+                if (NH == 2) tma_load_3d(qs + HALF_BYTES, &map_q, 64, t.g * rep, t.t_first + t.tq0, smem_u32(&bars->q_full));
                 it++;
                 for (int j = 0; j < t.n_iter; j++, jj++) {
                     const int s = jj % KV_STAGES;
@@ -381,20 +391,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         pg[h] = page;
                     }
                     if (!mbar_wait(smem_u32(&bars->s_full[s]), ph ^ 1u, abort_flag, status, 1)) { ok = false; break; }   // the scores of block jj - 2 are done
-                    mbar_expect_tx(smem_u32(&bars->k_full[s]), TILE_BYTES);
+                    mbar_expect_tx(smem_u32(&bars->k_full[s]), NH * HALF_BYTES);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {                       // page h -> rows 64h .. 64h+63 of both halves
                         const int row = (pg[h] * G + t.g) * PAGE;
                         tma_load_2d(ks + s * TILE_BYTES + h * (PAGE * 128), &map_k, 0, row, smem_u32(&bars->k_full[s]));
-                        tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
+                        if (NH == 2) tma_load_2d(ks + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_k, 64, row, smem_u32(&bars->k_full[s]));
                     }
                     if (!mbar_wait(smem_u32(&bars->pv_done[s]), ph ^ 1u, abort_flag, status, 2)) { ok = false; break; }   // P V of block jj - 2 is done
-                    mbar_expect_tx(smem_u32(&bars->v_full[s]), TILE_BYTES);
+                    mbar_expect_tx(smem_u32(&bars->v_full[s]), NH * HALF_BYTES);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const int row = (pg[h] * G + t.g) * PAGE;
                         tma_load_2d(vs + s * TILE_BYTES + h * (PAGE * 128), &map_v, 0, row, smem_u32(&bars->v_full[s]));
-                        tma_load_2d(vs + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_v, 64, row, smem_u32(&bars->v_full[s]));
+                        if (NH == 2) tma_load_2d(vs + s * TILE_BYTES + HALF_BYTES + h * (PAGE * 128), &map_v, 64, row, smem_u32(&bars->v_full[s]));
                     }
                 }
             }
@@ -402,7 +412,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16(ROWS, KEYS, 0);
-            constexpr uint32_t idesc_o = idesc_bf16(ROWS, D, 1);
+            constexpr uint32_t idesc_o = idesc_bf16(ROWS, DH, 1);
             uint32_t jj = 0, it = 0;
             bool ok = true;
             auto issue_s = [&](uint32_t u, bool last_of_item) -> bool {   // S of key block number u (running count)
@@ -411,7 +421,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!mbar_wait(smem_u32(&bars->s_empty[sb]), ((u >> 1) & 1u) ^ 1u, abort_flag, status, 4)) return false;
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 8; k++) {
+                for (int k = 0; k < DH / 16; k++) {
                     const uint32_t off = (k >> 2) * HALF_BYTES;
                     umma_ss(tmem + COL_S + sb * 128, desc_kmajor(qs + off) + 2 * (k & 3),
                             desc_kmajor(ks + s * TILE_BYTES + off) + 2 * (k & 3), idesc_s, k != 0);
@@ -470,7 +480,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = mbar_wait(smem_u32(&bars->s_full[sb]), (jj >> 1) & 1u, abort_flag, status, 8);
                 if (!ok) break;
                 tc_fence_after();
-                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.first_lo || window > 0 || t.nq * rep < ROWS;
+                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.first_lo || window > 0 || t.nq < TQ;
                 // this warp's half of the row into registers
                 uint32_t raw[2][32];
                 tmem_ld32_issue(lane_base + COL_S + sb * 128 + half * 64, raw[0]);
@@ -546,12 +556,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < 2; c++) {
+                    for (int c = 0; c < NH; c++) {
                         float o[32];
-                        tmem_ld32(lane_base + COL_O + half * 64 + c * 32, o);
+                        tmem_ld32(lane_base + COL_O + half * (DH / 2) + c * 32, o);
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] *= corr;
-                        tmem_st32(lane_base + COL_O + half * 64 + c * 32, o);
+                        tmem_st32(lane_base + COL_O + half * (DH / 2) + c * 32, o);
                     }
                 }
                 tmem_wait_st();
@@ -577,11 +587,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             it++;
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const int head = t.g * rep + (r - tq * rep);
-            __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * D + half * 64;   // each warp stores its 64 columns
+            __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * DH + half * (DH / 2);   // each warp stores its half of the columns
 #pragma unroll 1
-            for (int c = 0; c < 2; c++) {
+            for (int c = 0; c < NH; c++) {
                 float v[32];
-                tmem_ld32(lane_base + COL_O + half * 64 + c * 32, v);   // warp-collective: also for idle rows
+                tmem_ld32(lane_base + COL_O + half * (DH / 2) + c * 32, v);   // warp-collective: also for idle rows
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -646,6 +656,12 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rep = H / G;
     const int TQ = ROWS / rep;
+    for (int i = threadIdx.x; i < 2 * (ROWS - TQ * rep) * 16; i += blockDim.x) {      // both tiles' idle rows, as in the one-tile kernel
+        const int x = i / ((ROWS - TQ * rep) * 16), k = i - x * (ROWS - TQ * rep) * 16;
+        const int row = TQ * rep + (k >> 4), chunk = k & 15;
+        *reinterpret_cast<uint4*>(aligned + x * TILE_BYTES + (chunk >> 3) * HALF_BYTES + row * 128 + (chunk & 7) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     int seq = -1, tq0 = 0;
     {
         int left = (int)gridDim.x - 1 - (int)blockIdx.x;                 // long tiles first
@@ -829,7 +845,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             ok = mbar_wait(smem_u32(&bars->s_full[x]), n_done & 1u, abort_flag, status, 8);
             if (!ok) break;
             tc_fence_after();
-            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < first_lo || window > 0 || nq[x] * rep < ROWS;
+            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < first_lo || window > 0 || nq[x] < TQ;
             float v[4][32];
             tmem_ld_row128(lane_base + col_s, v);
             if (need_mask) {
@@ -954,17 +970,18 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
                                 const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                                 int tiles, int max_blocks, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (page_size != PAGE || d != D) return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim %d", PAGE, D);
+    if (page_size != PAGE || (d != 64 && d != 128))
+        return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim 64 or 128, got %d and %d", PAGE, page_size, d);
     if (G <= 0 || H % G) return gfb_fail("gfb_attn_prefill_tc: %d heads over %d groups", H, G);
     const int rep = H / G;
-    if (rep > 8 || ROWS % rep) return gfb_fail("gfb_attn_prefill_tc: %d heads per group (1, 2, 4 or 8)", rep);
+    if (rep > 8) return gfb_fail("gfb_attn_prefill_tc: %d heads per group (at most 8)", rep);
     const int TQ = ROWS / rep;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return gfb_fail("gfb_attn_prefill_tc: the driver does not export cuTensorMapEncodeTiled");
     CUtensorMap mq, mk, mv;
     {
-        cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)n_tokens};
-        cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2};
+        cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)H, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)H * d * 2};
         cuuint32_t box[3] = {64, (cuuint32_t)rep, (cuuint32_t)TQ};
         cuuint32_t es[3] = {1, 1, 1};
         CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
@@ -973,8 +990,8 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
         if (r != CUDA_SUCCESS) return gfb_fail("gfb_attn_prefill_tc: tensor map of q refused (%d)", (int)r);
     }
     for (int i = 0; i < 2; i++) {
-        cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)n_pages * G * PAGE};
-        cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+        cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)n_pages * G * PAGE};
+        cuuint64_t strides[1] = {(cuuint64_t)d * 2};
         cuuint32_t box[2] = {64, (cuuint32_t)PAGE};
         cuuint32_t es[2] = {1, 1};
         CUresult r = enc(i ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, i ? v_pool : k_pool, dims, strides, box, es,
@@ -991,7 +1008,7 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
     }
     cudaError_t e;
     const long blocks2 = ((long)(n_tokens + 2 * TQ - 1) / (2 * TQ)) * G;
-    if (tiles == 2 || (tiles == 0 && blocks2 >= 6L * sms)) {
+    if (d == 128 && (tiles == 2 || (tiles == 0 && blocks2 >= 6L * sms))) {
         // enough work for several rounds of blocks of two tiles, which share their K/V loads and keep the tensor
         // pipe busier (measured: from about 7,000 tokens of one sequence on, at 32 heads in 8 groups); with less
         // work the persistent one-tile kernel balances the SMs better
@@ -1007,18 +1024,23 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
                        page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
     } else {
         size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
-        static size_t configured = 0;
-        if (smem > configured) {
-            cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t a = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (a == cudaSuccess) a = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (a != cudaSuccess) return gfb_fail("gfb_attn_prefill_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(a));
-            configured = smem;
+            configured = true;
         }
         const int n_x = (n_tokens + TQ - 1) / TQ + n_seqs;           // an upper bound of the tiles; surplus items are empty
         long blocks = (long)n_x * G;
         const long cap = max_blocks > 0 ? max_blocks : sms;           // one block per SM walks over the items
         if (blocks > cap) blocks = cap;
-        e = gfb_launch(attn_prefill_tc_kernel, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
+        if (d == 128)
+            e = gfb_launch(attn_prefill_tc_kernel<128>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
+        else
+            e = gfb_launch(attn_prefill_tc_kernel<64>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
     }
     return gfb_check(e, "gfb_attn_prefill_tc");
 }

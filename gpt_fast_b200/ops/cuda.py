@@ -68,7 +68,6 @@ class CudaKernels:
         if not torch.cuda.is_available():
             _fail("no CUDA device: this library has no CPU path")
         self._fn = {}
-        self.use_tc_attention = True       # tcgen05 prefill attention where it fits; False: the mma.sync kernel
         self._sm_count = None
         self._status = None
         self.trace = None                  # a list: (label, start event, stop event) of every launch is appended
@@ -266,15 +265,10 @@ class CudaKernels:
         T = batch.n_tokens
         if prefill is None:
             prefill = splits is None and batch.max_q_len > 1 and head_dim in (64, 128)
-        if prefill and head_dim == 128 and (n_head // n_kv) in (1, 2, 4, 8) and self.use_tc_attention:
+        if prefill and head_dim in (64, 128) and n_head // n_kv <= 8:
             self._call("attention_tc", "gfb_attn_prefill_tc", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
                        c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(tiles),
                        c_int(max_blocks), _ptr(batch.status), _stream())
-            return
-        if prefill:
-            self._call("attention_bf16", "gfb_attn_prefill", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
-                       c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0),
-                       _ptr(batch.status), _stream())
             return
         if splits is None:
             splits = 1

@@ -78,6 +78,10 @@ PREFILL_CASES = [  # H, G, d, q_lens, starts
     (16, 2, 128, [33, 64], [1000, 7]),                # 8 heads per group
     (32, 8, 128, [700], [0]),                         # many key blocks per tile, from position 0
     (8, 2, 128, [300, 150, 64], [500, 1000, 129]),    # long contexts: blocks far below the diagonal
+    (24, 8, 128, [200, 45, 3, 129], [0, 5, 64, 1000]),  # head_dim 128, 3 heads per group on the tcgen05 kernel: 42 tokens, 126 rows
+    (10, 2, 128, [131, 77], [90, 0]),                 # 5 per group: 25 tokens, 125 rows
+    (12, 2, 128, [260], [300]),                       # 6 per group: 21 tokens, 126 rows
+    (7, 1, 128, [100, 20], [37, 640]),                # 7 per group: 18 tokens, 126 rows
 ]
 
 
