@@ -14,8 +14,8 @@ from .engine.model import Transformer
 from .engine.step import DecodeBatch, Stepper
 from .sampling import SamplingParams, sample
 from .weights.loader import WeightError
-from .weights.random_init import write_model_folder
+from .weights.random_init import save_folder, write_model_folder
 
 __all__ = ["load", "generate", "sample", "SamplingParams", "Transformer", "Stepper", "DecodeBatch", "ModelArgs",
-           "ConfigError", "WeightError", "write_model_folder", "named_configs", "config_from_name",
+           "ConfigError", "WeightError", "write_model_folder", "save_folder", "named_configs", "config_from_name",
            "architecture_names"]

@@ -48,11 +48,11 @@ def interleave_rotary_rows(n_heads: int, head_dim: int):
 
 
 def half_split_rotary_rows(n_heads: int, head_dim: int):
-    """Inverse of `interleave_rotary_rows` (used when a folder is written)."""
-    def combine(w):
+    """Inverse of `interleave_rotary_rows`: the recipe's `split`, used when a model is written to a folder."""
+    def split(w):
         cols = w.shape[1]
-        return w.view(n_heads, head_dim // 2, 2, cols).transpose(1, 2).reshape(n_heads * head_dim, cols)
-    return combine
+        return [w.view(n_heads, head_dim // 2, 2, cols).transpose(1, 2).reshape(n_heads * head_dim, cols)]
+    return split
 
 
 def weight_plan(a: ModelArgs) -> WeightPlan:
@@ -62,8 +62,10 @@ def weight_plan(a: ModelArgs) -> WeightPlan:
     for i in range(a.n_layer):
         s, t = f"model.layers.{i}.", f"layers.{i}."
         r += [
-            Recipe(t + "mixer.wq", [Source(s + "self_attn.q_proj.weight", (H * d, D))], interleave_rotary_rows(H, d)),
-            Recipe(t + "mixer.wk", [Source(s + "self_attn.k_proj.weight", (G * d, D))], interleave_rotary_rows(G, d)),
+            Recipe(t + "mixer.wq", [Source(s + "self_attn.q_proj.weight", (H * d, D))], interleave_rotary_rows(H, d),
+                   half_split_rotary_rows(H, d)),
+            Recipe(t + "mixer.wk", [Source(s + "self_attn.k_proj.weight", (G * d, D))], interleave_rotary_rows(G, d),
+                   half_split_rotary_rows(G, d)),
             Recipe(t + "mixer.wv", [Source(s + "self_attn.v_proj.weight", (G * d, D))]),
             Recipe(t + "mixer.wo", [Source(s + "self_attn.o_proj.weight", (D, H * d))]),
             Recipe(t + "feed_forward.w1", [Source(s + "mlp.gate_proj.weight", (I, D))]),

@@ -47,4 +47,6 @@ def load(source: Union[str, os.PathLike, dict], dtype="bfloat16", device="cuda",
     params = load_parameters(plan, ckpt, model.param_specs(), dt, device, progress)
     model.load_params(params)
     model.args = args
+    model.config = cfg                     # the config.json it was built from
+    model.weight_plan = plan
     return model

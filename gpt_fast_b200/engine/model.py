@@ -91,6 +91,20 @@ class Transformer:
             for pname, part in b.parts().items():
                 part.load(sub(f"layers.{i}.{pname}."))
 
+    def export_params(self) -> Dict[str, torch.Tensor]:
+        """Every parameter under the name and in the layout of `param_specs` (the inverse of `load_params`);
+        each part gives its own back through `export()`."""
+        out = {"embed.weight": self.embed_weight, "head.weight": self.head_weight}
+        for name, t in self.final_norm.export().items():
+            out[f"final_norm.{name}"] = t
+        for i, b in enumerate(self.blocks):
+            for pname, part in b.parts().items():
+                if not hasattr(part, "export"):
+                    raise NotImplementedError(f"part '{pname}' of layer {i} ({type(part).__name__}) has no export()")
+                for name, t in part.export().items():
+                    out[f"layers.{i}.{pname}.{name}"] = t
+        return out
+
     def weight_bytes(self, with_embedding=False) -> int:
         """Bytes of the parameters a decode step streams (every matrix once)."""
         seen, total = set(), 0

@@ -40,6 +40,12 @@ class Attention:
         self.wqkv = torch.cat([tensors["wq"], tensors["wk"], tensors["wv"]]).contiguous()
         self.wo = tensors["wo"]
 
+    def export(self):
+        """The parameters as `load` received them (the way back from the fused layout)."""
+        H, G, d = self.n_head, self.n_kv, self.head_dim
+        wq, wk, wv = self.wqkv.split([H * d, G * d, G * d])
+        return {"wq": wq, "wk": wk, "wv": wv, "wo": self.wo}
+
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(kv=KVNeed(self.n_kv, self.head_dim, self.window))
 

@@ -25,6 +25,11 @@ class SwiGLU:
         self.w13 = torch.stack([tensors["w1"], tensors["w3"]], dim=1).reshape(2 * self.hidden, self.dim).contiguous()
         self.w2 = tensors["w2"]
 
+    def export(self):
+        """The parameters as `load` received them (gate and up rows taken apart again)."""
+        w = self.w13.view(self.hidden, 2, self.dim)
+        return {"w1": w[:, 0], "w3": w[:, 1], "w2": self.w2}
+
     def forward(self, h, residual):
         act = torch.empty(h.shape[0], self.hidden, dtype=self.dtype, device=h.device)
         ops.linear(h, self.w13, act, mode="swiglu")

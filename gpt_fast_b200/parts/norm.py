@@ -20,6 +20,9 @@ class RMSNorm:
     def load(self, tensors):
         self.weight = tensors["weight"]
 
+    def export(self):
+        return {"weight": self.weight}
+
     def forward(self, x, out, rows=None):
         """x: the residual stream (a `Residual`, or a complete float32 tensor
         [T, dim]) -> out [R, dim] in the compute dtype; `rows` (int32 [R]) picks

@@ -21,10 +21,13 @@ class Source:
 @dataclass(frozen=True)
 class Recipe:
     """Model parameter `target` = combine(*sources).  `combine=None` takes the
-    only source as it is."""
+    only source as it is.  `split` is the way back, for writing a model out:
+    split(target tensor) -> the source tensors in order (None with `combine=None`:
+    the tensor itself; a recipe with a `combine` and no `split` cannot be written)."""
     target: str
     sources: Sequence[Source]
     combine: Optional[Callable] = None
+    split: Optional[Callable] = None
 
 
 @dataclass

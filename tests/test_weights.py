@@ -56,7 +56,7 @@ def test_rotary_row_permutation_is_the_stated_index_map():
         for i in range(d // 2):
             for j in range(2):
                 assert out[h * d + 2 * i + j, 0] == h * d + j * d // 2 + i
-    assert torch.equal(half_split_rotary_rows(H, d)(out), w)
+    assert torch.equal(half_split_rotary_rows(H, d)(out)[0], w)
 
 
 def test_tied_output_is_one_buffer_and_untied_is_two(tiny_folders):
@@ -145,3 +145,27 @@ def test_random_weights_mode_is_seeded_per_tensor(tmp_path):
     assert abs(ta["model.norm.weight"].float().mean() - 1.0) < 0.05
     cfg = json.load(open(os.path.join(a, "config.json")))
     assert cfg["hidden_size"] == 64 and cfg["model_type"] == "llama"
+
+
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_a_loaded_model_written_back_is_the_same_folder(tiny_folders, tmp_path, name):
+    """load -> save_folder -> load: the same tensors under the same checkpoint names (q/k rows back in half-split
+    order, gate/up and q/k/v taken apart again, the tied output not written twice), bit for bit, and the same
+    model parameters after loading the written folder."""
+    folder = tiny_folders[name]
+    model = gf.load(folder, dtype="bfloat16", device="cpu")
+    out = gf.save_folder(model, str(tmp_path / "written"))
+    a = load_file(os.path.join(folder, "model.safetensors"))
+    b = load_file(os.path.join(out, "model.safetensors"))
+    assert sorted(a) == sorted(b)
+    for k in a:
+        want = a[k] if a[k].dtype == torch.float32 and a[k].ndim == 1 else a[k].to(torch.bfloat16)
+        assert b[k].dtype == want.dtype and torch.equal(b[k], want), k
+    assert json.load(open(os.path.join(out, "config.json")))["num_hidden_layers"] == read_config(folder)["num_hidden_layers"]
+    again = gf.load(out, dtype="bfloat16", device="cpu")
+    pa, pb = model.export_params(), again.export_params()
+    assert sorted(pa) == sorted(pb) and all(torch.equal(pa[k], pb[k]) for k in pa)
+    # a model that was not made by load() cannot be written: it has no plan
+    bare = Transformer(model.spec, torch.bfloat16, "cpu")
+    with pytest.raises(ValueError, match="made by load"):
+        gf.save_folder(bare, str(tmp_path / "bare"))
