@@ -113,15 +113,16 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
     for (int i = c0 + 4 * threadIdx.x; i < c0 + chunk; i += 4 * blockDim.x) {
         float4 v = *reinterpret_cast<const float4*>(x + row + i);
         if (pending != nullptr) {
-            // four partial sums in flight together (the last group repeats its last load instead of branching);
-            // they are added in ascending order all the same
-            for (int k = 0; k < S; k += 4) {
-                float4 p[4];
+            // twelve partial sums in flight together, which covers the 8 or 9 of a decode step in one trip to L2 (the
+            // last group repeats its last load instead of branching); they are added in ascending order all the same
+            constexpr int W = 12;
+            for (int k = 0; k < S; k += W) {
+                float4 p[W];
 #pragma unroll
-                for (int u = 0; u < 4; u++)
+                for (int u = 0; u < W; u++)
                     p[u] = *reinterpret_cast<const float4*>(pending + (size_t)min(k + u, S - 1) * slice + row + i);
 #pragma unroll
-                for (int u = 0; u < 4; u++)
+                for (int u = 0; u < W; u++)
                     if (k + u < S) { v.x += p[u].x; v.y += p[u].y; v.z += p[u].z; v.w += p[u].w; }
             }
             *reinterpret_cast<float4*>(x + row + i) = v;

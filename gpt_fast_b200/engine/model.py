@@ -105,6 +105,12 @@ class Transformer:
                     out[f"layers.{i}.{pname}.{name}"] = t
         return out
 
+    def graph_safe(self) -> bool:
+        """Whether a step of this model may be captured in a CUDA graph: every part launches kernels only.  A part
+        that reads device values on the host says so with `graph_safe = False`."""
+        parts = [self.final_norm] + [p for b in self.blocks for p in b.parts().values()] + list(self.positions)
+        return all(getattr(p, "graph_safe", True) for p in parts + list(self.blocks))
+
     def weight_bytes(self, with_embedding=False) -> int:
         """Bytes of the parameters a decode step streams (every matrix once)."""
         seen, total = set(), 0

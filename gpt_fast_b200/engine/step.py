@@ -160,7 +160,9 @@ class DecodeBatch:
                                status=stepper.status)
         self.sampler = sampler
         self.logits = None
-        self.use_graph = use_graph and dev.type == "cuda"
+        # a part that looks at device values on the host (`graph_safe = False` on its class or instance) cannot be
+        # captured: the step then runs eagerly, launch by launch, with the same results
+        self.use_graph = use_graph and dev.type == "cuda" and self.model.graph_safe()
         self.graph = None
         self.steps_run = 0
 

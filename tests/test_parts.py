@@ -138,6 +138,7 @@ def test_swiglu_part(backend, dim, hidden):
 class RunningMeanMixer:
     """y_t = (decay * s + h_t) W with s the previous such sum of the sequence: a
     recurrent mixer whose only memory is a fixed-size state per sequence."""
+    graph_safe = False           # it reads the batch's bookkeeping on the host: a step with it is not captured
 
     def __init__(self, dim, decay, dtype, position=None):
         self.dim, self.decay, self.dtype = dim, decay, dtype
@@ -250,6 +251,18 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(backend):
         judge(whole[o:o + len(s)], want[i], emu[i], dtype, f"whole, sequence {i}")
         judge(torch.stack(rows[i]), want[i], emu[i], dtype, f"stepped, sequence {i}")
         o += len(s)
+    # the generation loop asks for a captured decode step; the mixer says it cannot be captured, so the loop runs the
+    # steps eagerly and gives the plain implementation's greedy tokens
+    assert not model.graph_safe()
+    out, stats = gf.generate(model, [seqs[0][:5]], 4, temperature=0.0, use_graph=True, stop_tokens=[])
+    seq = list(seqs[0][:5])
+    for _ in range(4):
+        logits = toy_plain(seq, P, spec)[-1]
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) < (1e-4 if dtype == torch.float32 else 0.05):
+            break                                    # a near tie: either token is right from here on
+        seq.append(int(logits.argmax()))
+    assert out[0][:len(seq)] == seq
 
 
 # ---- two more toy parts: another position encoding (used by a mixer of its own) and a routed feed-forward ----
