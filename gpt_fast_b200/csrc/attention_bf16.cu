@@ -28,6 +28,17 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
+// The same with an L2 policy: a decode step reads every cached key and value once, so their lines are marked to be
+// evicted first and leave L2 to what is read again within the step.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void cp_async16_hint(void* smem, const void* gmem, uint64_t pol) {
+    uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "l"(pol) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -320,6 +331,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     };
     bool bad_page = false;                       // uniform over the block
     int bad_index = 0;
+    const uint64_t kv_policy = l2_evict_first_policy();
     auto issue = [&](int page_index, int buf) {
         int page = (page_index >= 0 && page_index < kv.max_pages) ? pt[page_index] : -1;
         if (page < 0 || page >= kv.n_pages) {
@@ -333,8 +345,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         __nv_bfloat16* vd = tiles + (2 * buf + 1) * TILE;
         for (int c = tid; c < PAGE * (D / 8); c += THREADS) {
             int row = c / (D / 8), cc = c - row * (D / 8);
-            cp_async16(kd + row * PITCH + cc * 8, ksrc + row * D + cc * 8);
-            cp_async16(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8);
+            cp_async16_hint(kd + row * PITCH + cc * 8, ksrc + row * D + cc * 8, kv_policy);
+            cp_async16_hint(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8, kv_policy);
         }
     };
     // DECODE_NBUF - 1 pages in flight while q is prepared and, later, while a page is worked on

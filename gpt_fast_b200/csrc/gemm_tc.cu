@@ -97,6 +97,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
+// The same with an L2 policy: weights of a decode step are read once per step and are far larger than L2, so they
+// are marked to be evicted first and leave the cache to what is read again soon (activations, partial sums, the
+// key/value pages).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
 // 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
@@ -274,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         for (int i = 0; i < n_pre; i++) {                   // fresh barriers: every stage is free
             uint32_t full = smem_u32(&bars->full[i]);
             mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
-            if (SWAP) tma_load_2d(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
+            if (SWAP) tma_load_2d_hint(xs + i * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full, l2_evict_first_policy());
             else tma_load_2d(ys + i * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
         }
     }
@@ -297,6 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             const int n_pre = min(stages, nkb);             // their weight halves are on their way already
+            const uint64_t pol = l2_evict_first_policy();
             gfb_pdl_wait();
             for (int i = 0; i < n_pre; i++) {
                 uint32_t full = smem_u32(&bars->full[i]);
@@ -309,7 +324,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
                 uint32_t full = smem_u32(&bars->full[s]);
                 mbar_expect_tx(full, X_TILE_BYTES + Y_TILE_BYTES);
-                tma_load_2d(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
+                if (SWAP) tma_load_2d_hint(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full, pol);
+                else tma_load_2d(xs + s * X_TILE_BYTES, &map_x, (kb0 + i) * BK, row0, full);
                 tma_load_2d(ys + s * Y_TILE_BYTES, &map_y, (kb0 + i) * BK, col0, full);
             }
         }
