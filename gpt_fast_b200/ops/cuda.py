@@ -211,6 +211,8 @@ class CudaKernels:
             splits = max(1, min(total_kb // 8, (2 * self.sm_count) // blocks))
             stage = 16384 + bn * 128
             stages = max(2, min(8, (100 * 1024) // stage))
+            if blocks > 4 * self.sm_count:
+                stages = 3          # many rounds of blocks (the output product): four short rings per SM stream better than two long ones
             return 1, bn, splits, stages
         if N >= 256:
             # pairs of SMs on 256 x 256 tiles (bn 1024 = the cta_group::2 kernel), persistent, two
