@@ -55,14 +55,14 @@ class ModelSpec:
     max_position: int = 0                 # longest sequence the model allows
     stop_tokens: tuple = ()               # default stop tokens of generation
     bos_token: Optional[int] = None
-    embed_scale: Optional[float] = None   # factor on the embedding rows; no kernel takes one yet, so only None builds
-    logit_cap: Optional[float] = None     # soft cap on the logits; likewise
+    embed_scale: Optional[float] = None   # factor on the embedding rows (None: 1)
+    logit_cap: Optional[float] = None     # soft cap on the logits, cap * tanh(logits / cap) (None: none)
 
     def validate(self) -> None:
-        for name in ("embed_scale", "logit_cap"):
-            if getattr(self, name) is not None:
-                raise ValueError(f"ModelSpec.{name} = {getattr(self, name)}: no kernel of this library applies it yet; "
-                                 "refusing rather than ignoring it")
+        if self.logit_cap is not None and not self.logit_cap > 0:
+            raise ValueError(f"ModelSpec.logit_cap = {self.logit_cap}: a soft cap must be positive")
+        if self.embed_scale is not None and self.embed_scale != self.embed_scale:
+            raise ValueError("ModelSpec.embed_scale is not a number")
         owners = {}
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):

@@ -12,7 +12,7 @@ GFB_DEFINE_LAST_ERROR()
 // ---------------------------------------------------------------- embedding --
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int D, int V, int* status) {
+                             float* __restrict__ out, int D, int V, float scale, int* status) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     int t = blockIdx.x;
@@ -24,18 +24,19 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
         return;
     }
     const TW* row = table + (size_t)id * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_to_f32(row[i]);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_to_f32(row[i]) * scale;     // scale 1 changes no bit
 }
 
-GFB_API int gfb_embed(const int* tokens, const void* table, int table_dt, float* out, int T, int D, int V,
+// out[t] = table[tokens[t]] * scale, widened to 32-bit (scale: an architecture's factor on its embeddings; 1 for Llama).
+GFB_API int gfb_embed(const int* tokens, const void* table, int table_dt, float* out, int T, int D, int V, float scale,
                       int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     int threads = D >= 1024 ? 256 : 128;
     cudaError_t e;
     if (table_dt == GFB_BF16)
-        e = gfb_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, D, V, status);
+        e = gfb_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, D, V, scale, status);
     else if (table_dt == GFB_F32)
-        e = gfb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, D, V, status);
+        e = gfb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, D, V, scale, status);
     else
         return gfb_fail("gfb_embed: unknown table type %d", table_dt);
     return gfb_check(e, "gfb_embed");
@@ -506,4 +507,19 @@ GFB_API int gfb_add_into(float* out, const void* y, int dt, long n, cudaStream_t
     else if (dt == GFB_F32) e = gfb_launch(add_into_kernel<float>, dim3(blocks), dim3(256), 0, stream, out, (const float*)y, (size_t)n);
     else return gfb_fail("gfb_add_into: unknown type %d", dt);
     return gfb_check(e, "gfb_add_into");
+}
+
+// x = cap * tanh(x / cap), in 32-bit, in place: a soft cap on logits (an architecture's option; Llama has none).
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+GFB_API int gfb_softcap(float* x, long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return gfb_fail("gfb_softcap: the cap must be positive, got %g", (double)cap);
+    cudaError_t e = gfb_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, (size_t)n, cap);
+    return gfb_check(e, "gfb_softcap");
 }

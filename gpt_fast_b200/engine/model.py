@@ -176,7 +176,7 @@ class Transformer:
         and values to the cache; the caller advances the lengths afterwards."""
         T = batch.n_tokens
         x = torch.empty(T, self.dim, dtype=torch.float32, device=self.device)
-        ops.embed(tokens, self.embed_weight, x, batch.status)
+        ops.embed(tokens, self.embed_weight, x, batch.status, 1.0 if self.spec.embed_scale is None else float(self.spec.embed_scale))
         x = Residual(x)
         for e in self.spec.schedule:
             self.blocks[e.layer].forward(x, batch, cache.view(e.cache), append=e.owns_cache)
@@ -186,4 +186,6 @@ class Transformer:
             h = torch.empty(W, self.dim, dtype=self.dtype, device=self.device)
             self.final_norm.forward(x, h, want_rows)
             ops.linear(h, self.head_weight, logits)
+            if self.spec.logit_cap is not None:
+                ops.softcap(logits, float(self.spec.logit_cap))
         return logits

@@ -86,10 +86,15 @@ def check_status(status: torch.Tensor) -> None:
 
 # ---- the operations ---------------------------------------------------------------
 
-def embed(tokens, table, out, status):
-    """out[t] = table[tokens[t]] widened to 32-bit.  tokens int32 [T]; table
+def embed(tokens, table, out, status, scale: float = 1.0):
+    """out[t] = table[tokens[t]] * scale widened to 32-bit.  tokens int32 [T]; table
     [V, D]; out float32 [T, D]."""
-    return kernels().embed(tokens, table, out, status)
+    return kernels().embed(tokens, table, out, status, scale)
+
+
+def softcap(x, cap: float):
+    """x (float32, in place) = cap * tanh(x / cap)."""
+    return kernels().softcap(x, cap)
 
 
 def rmsnorm(x, weight, eps: float, out, rows=None, pending=None):

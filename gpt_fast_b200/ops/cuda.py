@@ -99,14 +99,18 @@ class CudaKernels:
             _fail(f"{name}: {fn._lib.gfb_last_error().decode()}")
 
     # -- element-wise / per-row -------------------------------------------------
-    def embed(self, tokens, table, out, status):
+    def embed(self, tokens, table, out, status, scale=1.0):
         T = tokens.shape[0]
         V, D = table.shape
         _need(tokens, torch.int32, name="tokens")
         _need(table, name="embedding table")
         _need(out, torch.float32, (T, D), "embedding output")
         self._call("core", "gfb_embed", _ptr(tokens), _ptr(table), c_int(_dt(table)), _ptr(out),
-                   c_int(T), c_int(D), c_int(V), _ptr(status), _stream())
+                   c_int(T), c_int(D), c_int(V), c_float(scale), _ptr(status), _stream())
+
+    def softcap(self, x, cap):
+        _need(x, torch.float32, name="logits")
+        self._call("core", "gfb_softcap", _ptr(x), c_long(x.numel()), c_float(cap), _stream())
 
     def rmsnorm(self, x, weight, eps, out, rows=None, pending=None):
         D = x.shape[-1]

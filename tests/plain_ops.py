@@ -56,14 +56,17 @@ def race_noise(seed, request, token_index, V):
 
 class PlainOps:
     # -- element-wise / per-row ---------------------------------------------------
-    def embed(self, tokens, table, out, status):
+    def softcap(self, x, cap):
+        x.copy_((cap * torch.tanh(x.double() / cap)).float())
+
+    def embed(self, tokens, table, out, status, scale=1.0):
         ids = tokens.long()
         bad = (ids < 0) | (ids >= table.shape[0])
         if bad.any():
             t = int(bad.nonzero()[0])
             if status[0] == 0:
                 status[0], status[1], status[2] = 1, t, int(ids[t])
-        out.copy_(table[ids.clamp(0, table.shape[0] - 1)].float())
+        out.copy_(table[ids.clamp(0, table.shape[0] - 1)].float() * scale)
         out[bad] = 0
 
     def rmsnorm(self, x, weight, eps, out, rows=None, pending=None):

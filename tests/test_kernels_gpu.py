@@ -245,6 +245,26 @@ def test_advance_lengths_and_add_into():
         assert torch.equal(x, ref)
 
 
+def test_embed_scale_and_logit_softcap():
+    table = rnd(50, 72, dtype=torch.bfloat16)
+    tokens = torch.randint(0, 50, (9,), dtype=torch.int32, device=DEV)
+    out, ref = torch.empty(9, 72, device=DEV), torch.empty(9, 72, device=DEV)
+    st = ops.new_status(DEV)
+    ops.embed(tokens, table, out, st, 8.5)
+    REF.embed(tokens, table, ref, st.clone(), 8.5)
+    assert torch.equal(out, ref)                           # one 32-bit product of a widened value: exact
+    ops.embed(tokens, table, out, st)
+    assert torch.equal(out, table[tokens.long()].float())  # the default scale changes no bit
+    x = rnd(7, 1001, scale=20.0)
+    want = x.clone()
+    ops.softcap(x, 30.0)
+    REF.softcap(want, 30.0)
+    torch.testing.assert_close(x, want, rtol=2e-6, atol=2e-6)
+    assert float(x.abs().max()) <= 30.0
+    with pytest.raises(ops.KernelError, match="positive"):
+        ops.softcap(x, 0.0)
+
+
 @pytest.mark.parametrize("B,V", [(1, 256), (5, 320), (3, 128256), (2, 1001)])
 def test_argmax(B, V):
     logits = rnd(B, V)

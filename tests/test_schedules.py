@@ -235,7 +235,8 @@ class SharedNormBlock:
 
 
 def toy_arch_parse(cfg):
-    need = ("width", "heads", "kv_heads", "head_size", "inner", "depth", "vocab", "eps", "theta", "longest")
+    need = ("width", "heads", "kv_heads", "head_size", "inner", "depth", "vocab", "eps", "theta", "longest", "embed_scale",
+            "logit_cap")
     missing = [k for k in need if k not in cfg]
     if missing:
         raise gf.ConfigError(f"config.json: keys {missing} are required")
@@ -250,7 +251,8 @@ def toy_arch_spec(a):
         feed_forward=PartSpec("swiglu", dict(dim=a["width"], hidden=a["inner"]))),
         PartSpec("rope", dict(head_dim=a["head_size"], base=a["theta"], pairing="half")))
     return ModelSpec("parallel-toy", a["width"], a["vocab"], [layer] * a["depth"],
-                     [ScheduleEntry(i, i) for i in range(a["depth"])], norm, tie_embeddings=True, max_position=a["longest"])
+                     [ScheduleEntry(i, i) for i in range(a["depth"])], norm, tie_embeddings=True, max_position=a["longest"],
+                     embed_scale=a["embed_scale"], logit_cap=a["logit_cap"])
 
 
 def toy_arch_plan(a):
@@ -277,7 +279,7 @@ def toy_arch_plain(tokens, T, a, act=None):
     R = plain_llama.rounded
     D, H, G, d = a["width"], a["heads"], a["kv_heads"], a["head_size"]
     S = len(tokens)
-    x = T["wte"].float()[tokens]
+    x = T["wte"].float()[tokens] * a["embed_scale"]
     cos, sin = plain_llama.rope_angles(torch.arange(S), plain_llama.rope_frequencies(d, a["theta"]))
     for i in range(a["depth"]):
         s = f"h.{i}."
@@ -287,7 +289,8 @@ def toy_arch_plain(tokens, T, a, act=None):
         v = R((h @ T[s + "v"].float().T).view(S, G, d), act)
         y = R(windowed_attention(q, k, v, H, G, None), act) @ T[s + "o"].float().T
         x = x + y + plain_llama.feed_forward(h, T[s + "gate"].float(), T[s + "down"].float(), T[s + "up"].float(), act)
-    return plain_llama.rms_norm(x, T["ln_f"].float(), a["eps"], act) @ T["wte"].float().T
+    logits = plain_llama.rms_norm(x, T["ln_f"].float(), a["eps"], act) @ T["wte"].float().T
+    return a["logit_cap"] * torch.tanh(logits / a["logit_cap"])
 
 
 def test_an_architecture_registered_from_a_test_loads_from_its_folder_and_steps(backend, tmp_path):
@@ -298,7 +301,7 @@ def test_an_architecture_registered_from_a_test_loads_from_its_folder_and_steps(
                                            build_spec=toy_arch_spec, weight_plan=toy_arch_plan))
     assert "parallel-toy" in gf.architecture_names()
     cfg = dict(model_type="parallel-toy", width=80, heads=5, kv_heads=5, head_size=16, inner=136, depth=2, vocab=89,
-               eps=1e-6, theta=3000.0, longest=160)
+               eps=1e-6, theta=3000.0, longest=160, embed_scale=8.0, logit_cap=0.5)
     folder = gf.write_model_folder(str(tmp_path / "toy"), cfg, seed=21)
     with open(tmp_path / "toy" / "config.json") as f:
         assert json.load(f)["model_type"] == "parallel-toy"
