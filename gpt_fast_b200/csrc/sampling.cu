@@ -217,13 +217,44 @@ sample_row_kernel(const float* __restrict__ logits, int* __restrict__ out, int V
     bool gathered = false;                                   // uniform: the survivors are among cand_*[0 .. n)
     int n = 0;
     if (filter && top_k <= ROW_CAP / 2) {
-        // mean and deviation of the finite entries among the first ROW_SAMPLE of the row (vocabulary order carries
-        // no order of the logits; a poor guess only costs a repeated pass)
-        const int n_sample = V < ROW_SAMPLE ? V : ROW_SAMPLE;
+        // mean and deviation of the finite entries of a sample of the row: ROW_SAMPLE entries spread evenly over it
+        // (in groups of four; tokenizers put frequent tokens at low ids, so a prefix of the row could be far from
+        // typical).  A poor guess only costs a repeated pass.
         float s1 = 0.f, s2 = 0.f, cnt = 0.f;
-        for_row(row, n_sample, [&](int, float x) {              // raw logits: the division is kept for the few that matter
-            if (fabsf(x) < INFINITY) { s1 += x; s2 += x * x; cnt += 1.f; }
-        });
+        const int groups = V >> 2;                                   // whole groups of four entries
+        const int n_groups = groups < ROW_SAMPLE / 4 ? groups : ROW_SAMPLE / 4;
+        const int n_sample = n_groups > 0 ? 4 * n_groups : V;
+        if (n_groups > 0) {
+            const int stride = groups / n_groups;                    // >= 1
+            const bool aligned16 = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+            float x4[ROW_SAMPLE / 4 / ROW_THREADS][4];
+#pragma unroll
+            for (int j = 0; j < ROW_SAMPLE / 4 / ROW_THREADS; j++) {
+                const int gi = threadIdx.x + j * ROW_THREADS;
+                if (gi >= n_groups) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) x4[j][e] = INFINITY;
+                } else if (aligned16) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(row) + (size_t)gi * stride);
+                    x4[j][0] = v.x; x4[j][1] = v.y; x4[j][2] = v.z; x4[j][3] = v.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) x4[j][e] = row[(size_t)gi * stride * 4 + e];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < ROW_SAMPLE / 4 / ROW_THREADS; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float x = x4[j][e];
+                    if (fabsf(x) < INFINITY) { s1 += x; s2 += x * x; cnt += 1.f; }
+                }
+        } else {
+            for (int i = threadIdx.x; i < V; i += ROW_THREADS) {
+                const float x = row[i];
+                if (fabsf(x) < INFINITY) { s1 += x; s2 += x * x; cnt += 1.f; }
+            }
+        }
         s1 = gfb_block_sum(s1, sv);
         s2 = gfb_block_sum(s2, sv);
         cnt = gfb_block_sum(cnt, sv);
