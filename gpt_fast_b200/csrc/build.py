@@ -144,8 +144,21 @@ def library(name: str) -> ctypes.CDLL:
         return lib
 
 
-def build_all(names=None, verbose=True):
-    return {n: build(n, verbose) for n in (names or LIBRARIES) if _sources_exist(n)}
+def build_all(names=None, verbose=True, prune=True):
+    """Build every library (or `names`); with prune, builds of earlier source states are removed from the
+    folder the current ones went to, so that it holds one file per library."""
+    built = {n: build(n, verbose) for n in (names or LIBRARIES) if _sources_exist(n)}
+    if prune:
+        keep = {os.path.basename(p) for p in built.values()}
+        for folder in {os.path.dirname(p) for p in built.values()}:
+            for fn in os.listdir(folder):
+                stem = fn.split("-")[0]
+                if fn.endswith(".so") and stem in {f"libgfb_{n}" for n in built} and fn not in keep:
+                    try:
+                        os.remove(os.path.join(folder, fn))
+                    except OSError:
+                        pass
+    return built
 
 
 def _sources_exist(name):
