@@ -22,7 +22,7 @@ constexpr int MAX_REP = 8;          // query heads per key/value head
 constexpr int MAX_DPT = 2;          // head_dim <= THREADS * MAX_DPT
 // K/V tile pairs of the tensor-core decode kernel: NBUF - 1 pages are in flight per block.  3 lets two blocks share
 // an SM; 5 (one block per SM) is for small grids, where a short context is then requested all at once.
-constexpr int DECODE_NBUF_MANY = 3, DECODE_NBUF_FEW = 5;
+constexpr int DECODE_NBUF_MANY = 3, DECODE_NBUF_FEW = 5, DECODE_NBUF_SHORT = 2;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -615,10 +615,14 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const f
 // + the query rows of shared memory; the merge area reuses the tiles.
 cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, const void* q, void* out, float* so, float* sml,
                               GfbPagedKV kv, GfbBatch b, int H, int G, float scale, int window, int splits, int* status,
-                              RopeSource rs) {
+                              RopeSource rs, int pages_per_slice) {
     typedef void (*Kern)(const __nv_bfloat16*, __nv_bfloat16*, float*, float*, GfbPagedKV, GfbBatch, int, int, float, int, int,
                          int*, RopeSource);
-    static const Kern kerns[2][2][3] = {
+    // Tile pairs per block: five where the grid leaves at most one block per SM anyway (a short context is then
+    // requested all at once); two where there are several rounds of short blocks (a few pages each: three blocks
+    // fit an SM and their set-ups and merges overlap: 13B sizes at batch 32, 50 -> 42 us); three otherwise (long
+    // slices want two pages in flight behind the one being worked on).
+    static const Kern kerns[3][2][3] = {
         {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_MANY>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_MANY>,
           attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_MANY>},
          {attn_decode_mma_kernel<128, SRC_Q, DECODE_NBUF_MANY>, attn_decode_mma_kernel<128, SRC_QKV, DECODE_NBUF_MANY>,
@@ -626,16 +630,21 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
         {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_FEW>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_FEW>,
           attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_FEW>},
          {attn_decode_mma_kernel<128, SRC_Q, DECODE_NBUF_FEW>, attn_decode_mma_kernel<128, SRC_QKV, DECODE_NBUF_FEW>,
-          attn_decode_mma_kernel<128, SRC_PARTIALS, DECODE_NBUF_FEW>}}};
-    static bool configured[2][2][3] = {};
+          attn_decode_mma_kernel<128, SRC_PARTIALS, DECODE_NBUF_FEW>}},
+        {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_SHORT>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_SHORT>,
+          attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_SHORT>},
+         {attn_decode_mma_kernel<128, SRC_Q, DECODE_NBUF_SHORT>, attn_decode_mma_kernel<128, SRC_QKV, DECODE_NBUF_SHORT>,
+          attn_decode_mma_kernel<128, SRC_PARTIALS, DECODE_NBUF_SHORT>}}};
+    static bool configured[3][2][3] = {};
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
     }
     const int di = d == 128 ? 1 : 0;
-    const int few = (long)grid.x * grid.y * grid.z <= sms ? 1 : 0;      // at most one block per SM anyway
-    const int nbuf = few ? DECODE_NBUF_FEW : DECODE_NBUF_MANY;
+    const long blocks = (long)grid.x * grid.y * grid.z;
+    const int few = blocks <= sms ? 1 : (blocks >= 4L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
+    const int nbuf = few == 1 ? DECODE_NBUF_FEW : few == 2 ? DECODE_NBUF_SHORT : DECODE_NBUF_MANY;
     const size_t msmem = (size_t)(2 * nbuf * PAGE + 8) * (d + 8) * 2;
     Kern kern = kerns[few][di][src];
     if (msmem > 48 * 1024 && !configured[few][di][src]) {
@@ -683,7 +692,7 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     dim3 grid(n_tokens, G, splits);
     cudaError_t e;
     if (d == 128 || d == 64) {
-        e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, RopeSource{});
+        e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, RopeSource{}, 0);
         if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
     } else {
         e = gfb_launch(attn_decode_kernel, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
@@ -704,12 +713,14 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
 // With append = 0 only q is taken from it (the layer reads a cache that another layer wrote).
 // The kernel asks for its first pages before the preceding kernel has ended, on the lengths as they are then, and
 // reads the lengths again afterwards; lengths_early (optional, per slot like lengths) stands in for the first read,
-// which lets a test make the two differ.
+// which lets a test make the two differ.  max_kv_len (0: unknown): the longest sequence of the batch after this step,
+// as the host knows it; it only chooses how many pages a block keeps in flight.
 GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k_pool, void* v_pool, const int* page_table,
                                  int max_pages, int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq,
                                  const int* slots, const int* lengths, int n_seqs, int n_tokens, const float* table,
                                  int table_len, int H, int G, int d, int pairing, int append, float scale, int window,
-                                 int splits, float* scratch, int* status, const int* lengths_early, cudaStream_t stream) {
+                                 int splits, float* scratch, int* status, const int* lengths_early, int max_kv_len,
+                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (page_size != PAGE) return gfb_fail("gfb_attn_decode_rope: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
     if (d != 64 && d != 128) return gfb_fail("gfb_attn_decode_rope: head_dim %d (64 or 128)", d);
@@ -722,8 +733,9 @@ GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k
     float* so = scratch;
     float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
     RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append, lengths_early};
+    const int pages = max_kv_len > 0 ? (max_kv_len + PAGE - 1) / PAGE : 0;
     cudaError_t e = launch_decode_mma(d, n_part > 0 ? SRC_PARTIALS : SRC_QKV, dim3(n_tokens, G, splits), stream, nullptr, out, so, sml,
-                                      kv, b, H, G, scale, window, splits, status, rs);
+                                      kv, b, H, G, scale, window, splits, status, rs, (pages + splits - 1) / splits);
     if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
     if (gfb_check(e, "gfb_attn_decode_rope")) return 1;
     if (splits > 1) {

@@ -316,7 +316,7 @@ class CudaKernels:
         self._call("attention_bf16", "gfb_attn_decode_rope", _ptr(src), c_int(n_part), _ptr(out), *self._kv_args(kv),
                    *self._batch_args(batch), _ptr(table), c_int(table.shape[0]), c_int(n_head), c_int(n_kv), c_int(head_dim),
                    c_int(_PAIRING[pairing]), c_int(1 if append else 0), c_float(scale), c_int(window or 0), c_int(splits),
-                   _ptr(scratch), _ptr(batch.status), _ptr(lengths_early), _stream())
+                   _ptr(scratch), _ptr(batch.status), _ptr(lengths_early), c_int(int(batch.max_kv_len)), _stream())
         return True
 
     # -- sampling --------------------------------------------------------------------------
