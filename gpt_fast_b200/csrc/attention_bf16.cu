@@ -6,10 +6,13 @@
 // head, slice of the sequence's pages) and serves all query heads of the group
 // from one pass over the keys and values, so each cached byte is read once per
 // group, not once per head.  Pages (64 tokens x head_dim, contiguous per head)
-// are brought to shared memory with cp.async, several pages ahead.  Scores,
+// are brought to shared memory several pages ahead (cp.async; TMA in the
+// tensor-core version).  Scores,
 // softmax and the weighted sum are 32-bit.  With more than one slice per
 // sequence the blocks write (max, sum, unnormalised output) to scratch and
 // attn_combine merges the slices in ascending order.
+#include <cuda.h>
+
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
@@ -21,24 +24,50 @@ constexpr int THREADS = 128;
 constexpr int MAX_REP = 8;          // query heads per key/value head
 constexpr int MAX_DPT = 2;          // head_dim <= THREADS * MAX_DPT
 // K/V tile pairs of the tensor-core decode kernel: NBUF - 1 pages are in flight per block.  3 lets two blocks share
-// an SM; 5 (one block per SM) is for small grids, where a short context is then requested all at once.
+// an SM and 2 three; 5 (one block per SM) is for small grids, where a short context is then requested all at once.
 constexpr int DECODE_NBUF_MANY = 3, DECODE_NBUF_FEW = 5, DECODE_NBUF_SHORT = 2;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
-// The same with an L2 policy: a decode step reads every cached key and value once, so their lines are marked to be
-// evicted first and leave L2 to what is read again within the step.
+// A decode step reads every cached key and value once, so their lines are marked to be evicted first and leave L2
+// to what is read again within the step.
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
-__device__ __forceinline__ void cp_async16_hint(void* smem, const void* gmem, uint64_t pol) {
-    uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "l"(pol) : "memory");
+// A box of a page ([64 tokens][64 dims], 128-byte swizzle) by TMA; its bytes are counted on a shared-memory barrier.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol) : "memory");
 }
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* m) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    return v;
+}
+constexpr unsigned long long PAGE_WAIT_LIMIT_NS = 1000000000ull;   // a page that has not come after a second is given up
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -225,8 +254,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
 // the (up to 8) query heads of the group are rows 0..7 of the 16-row A operand.  Each of the
 // 4 warps owns 16 of a page's 64 keys and runs an online softmax of its own over them (no
 // block-wide exchange per page); the four partial results are merged once at the end.
-// K and V tiles sit in shared memory with rows padded by 16 bytes, so ldmatrix reads them
-// without bank conflicts; V is read with ldmatrix.trans.
+// K and V tiles are brought by TMA, one thread asking for a whole page, as halves of [64 tokens][64 dims] whose
+// 16-byte chunks are swizzled by the row (128-byte swizzle), so ldmatrix reads them without bank conflicts; V is
+// read with ldmatrix.trans.  (cp.async from all threads, 32 instructions per thread and page, kept an SM's two
+// blocks busy for 0.7 us per page with issuing alone.)
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -235,11 +266,22 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint3
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-// c += a * b with rows 8..15 of a equal to zero (a1 = a3 = 0)
+// c += a * b with rows 8..15 of a equal to zero (a1 = a3 = 0): only c[0], c[1] (rows 0..7) live on, the other two
+// results are zero and are dropped
 __device__ __forceinline__ void mma_rows8(float* c, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+    float z2, z3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %10};"
+                 : "+f"(c[0]), "+f"(c[1]), "=f"(z2), "=f"(z3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+    (void)z2;
+    (void)z3;
+}
+
+// Byte offset of element (row, col) in a tile of [64 rows][D] brought as D / 64 boxes with 128-byte swizzle: box
+// col / 64, row of 128 bytes, its 16-byte chunk exchanged by the row's low three bits.
+__device__ __forceinline__ uint32_t swz(int row, int col) {
+    const int box = col >> 6, chunk = (col >> 3) & 7;
+    return (uint32_t)(box * (PAGE * 128) + row * 128 + ((chunk ^ (row & 7)) << 4) + (col & 7) * 2);
 }
 
 // What the decode kernel starts from.  SRC_Q: q [T, H, D], rotated, and the cache already holds this step's
@@ -259,6 +301,7 @@ struct RopeSource {
     int append;               // 0: the layer reads a cache another layer wrote
     const int* lengths_early; // optional: the lengths to request the first pages on before the preceding kernel has
                               // ended (null: the batch's own); they are checked against the batch's own afterwards
+    int one_each;             // every sequence brings exactly one token: token t is sequence t (two loads fewer)
 };
 
 // x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
@@ -273,11 +316,24 @@ __device__ __forceinline__ void load_pairs(const RopeSource& r, const size_t* e0
         constexpr int W = 8;                                  // partial sums in flight together
         for (int k = 0; k < r.S; k += W) {
             float a[W][N], c[W][N];
+            if (r.pairing == 0) {                             // neighbours (e1 = e0 + 1, e0 even): one load of both
 #pragma unroll
-            for (int u = 0; u < W; u++) {
-                const float* pk = p + (size_t)min(k + u, r.S - 1) * r.slice;
+                for (int u = 0; u < W; u++) {
+                    const float* pk = p + (size_t)min(k + u, r.S - 1) * r.slice;
 #pragma unroll
-                for (int i = 0; i < N; i++) { a[u][i] = pk[e0[i]]; c[u][i] = pk[e1[i]]; }
+                    for (int i = 0; i < N; i++) {
+                        const float2 both = *reinterpret_cast<const float2*>(pk + e0[i]);
+                        a[u][i] = both.x;
+                        c[u][i] = both.y;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < W; u++) {
+                    const float* pk = p + (size_t)min(k + u, r.S - 1) * r.slice;
+#pragma unroll
+                    for (int i = 0; i < N; i++) { a[u][i] = pk[e0[i]]; c[u][i] = pk[e1[i]]; }
+                }
             }
 #pragma unroll
             for (int u = 0; u < W; u++)
@@ -288,35 +344,63 @@ __device__ __forceinline__ void load_pairs(const RopeSource& r, const size_t* e0
         }
     } else {
         const __nv_bfloat16* p = (const __nv_bfloat16*)r.src;
+        if (r.pairing == 0) {
 #pragma unroll
-        for (int i = 0; i < N; i++) { x0[i] = __bfloat162float(p[e0[i]]); x1[i] = __bfloat162float(p[e1[i]]); }
+            for (int i = 0; i < N; i++) {
+                const float2 both = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + e0[i]));
+                x0[i] = both.x;
+                x1[i] = both.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < N; i++) { x0[i] = __bfloat162float(p[e0[i]]); x1[i] = __bfloat162float(p[e1[i]]); }
+        }
     }
 }
 
 template <int D, int SRC, int DECODE_NBUF>
 __global__ void __launch_bounds__(THREADS)
-attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
                        GfbPagedKV kv, GfbBatch b, int H, int G, float scale_log2e, int window, int splits, int* status,
                        RopeSource rs) {
-    constexpr int PITCH = D + 8;                 // elements per shared-memory row
+    constexpr int PITCH = D + 8;                 // elements per row of q in shared memory
     constexpr int KSTEPS = D / 16, NT = D / 8;
-    constexpr int TILE = PAGE * PITCH;           // elements per tile
-    extern __shared__ __align__(16) uint8_t smem[];
-    __nv_bfloat16* tiles = (__nv_bfloat16*)smem;               // K0 V0 K1 V1 ... : DECODE_NBUF pairs
-    __nv_bfloat16* qs = tiles + 2 * DECODE_NBUF * TILE;        // [8][PITCH]
+    constexpr int HALF_BYTES = PAGE * 128;       // [64 tokens][64 dims]: one TMA box
+    constexpr int TILE_BYTES = PAGE * D * 2;     // the keys (or values) of a page: D / 64 boxes
+    constexpr int BOXES = 2 * D / 64;            // per page; each is asked for by another warp (at most THREADS / 32)
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const uint32_t raw_u32 = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t tiles_u32 = (raw_u32 + 1023u) & ~1023u;     // swizzled boxes start on 1024-byte boundaries
+    uint8_t* smem = smem_raw + (tiles_u32 - raw_u32);          // K0 V0 K1 V1 ... : DECODE_NBUF pairs
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem + 2 * DECODE_NBUF * TILE_BYTES);   // [8][PITCH]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(qs + 8 * PITCH);   // one barrier per tile pair: its page has arrived
+    int* gave_up = reinterpret_cast<int*>(bars + DECODE_NBUF);      // a wait ran out: results are void, the status says so
     gfb_pdl_launch();
     const int rep = H / G;
     const int t = blockIdx.x, g = blockIdx.y, z = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = lane >> 2, t4 = lane & 3;     // row (head) and column pair of the mma fragments
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+    if (tid == 0) {
+        prefetch_map(&map_k);
+        prefetch_map(&map_v);
+#pragma unroll
+        for (int i = 0; i < DECODE_NBUF; i++) mbar_init(bar0 + 8 * i, BOXES);
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
     // Before the wait for the preceding kernel: what only depends on earlier steps.  The batch's bookkeeping and the
     // page table are written by the host before the step; the sequence's length is advanced by the last kernel of the
     // previous step, which has almost certainly ended, so the pages are requested on the length read now and the
     // length is read again behind the wait.
-    const int s = b.tok_seq[t];
+    const bool one_each = SRC != SRC_Q && rs.one_each != 0;
+    const int s = one_each ? t : b.tok_seq[t];
     const int slot = b.slots[s];
-    const int q_off = t - b.cu_seqlens[s];
+    const int q_off = one_each ? 0 : t - b.cu_seqlens[s];
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
     int pos, lo, first_page, last_page, per, p0, p1;
     auto plan = [&](int len) {
@@ -331,42 +415,98 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
     };
     bool bad_page = false;                       // uniform over the block
     int bad_index = 0;
+    uint32_t parity_bits = 0, pending_bits = 0;  // per tile pair: the barrier phase to wait for; a page is on its way
     const uint64_t kv_policy = l2_evict_first_policy();
-    auto issue = [&](int page_index, int buf) {
-        int page = (page_index >= 0 && page_index < kv.max_pages) ? pt[page_index] : -1;
+    // The page table's entries are read one request ahead of the copies that need them (an entry beyond the
+    // sequence's pages is read but never used), so that no copy waits for a load of its address.
+    auto entry = [&](int page_index) -> int {
+        return (page_index >= 0 && page_index < kv.max_pages) ? __ldg(pt + page_index) : -1;
+    };
+    auto issue = [&](int page_index, int buf, int page) {
         if (page < 0 || page >= kv.n_pages) {
             bad_page = true;                     // reported once the length is certain
             bad_index = page_index;
             page = 0;
         }
-        const __nv_bfloat16* ksrc = (const __nv_bfloat16*)kv.k_pool + ((size_t)page * G + g) * PAGE * D;
-        const __nv_bfloat16* vsrc = (const __nv_bfloat16*)kv.v_pool + ((size_t)page * G + g) * PAGE * D;
-        __nv_bfloat16* kd = tiles + (2 * buf) * TILE;
-        __nv_bfloat16* vd = tiles + (2 * buf + 1) * TILE;
-        for (int c = tid; c < PAGE * (D / 8); c += THREADS) {
-            int row = c / (D / 8), cc = c - row * (D / 8);
-            cp_async16_hint(kd + row * PITCH + cc * 8, ksrc + row * D + cc * 8, kv_policy);
-            cp_async16_hint(vd + row * PITCH + cc * 8, vsrc + row * D + cc * 8, kv_policy);
+        pending_bits |= 1u << buf;
+        if (lane == 0 && warp < BOXES) {                     // one box per warp: its first lane announces and asks
+            const uint32_t bar = bar0 + 8 * buf;
+            const int y = (page * G + g) * PAGE;             // the page's first row in the pool seen as [rows][D]
+            mbar_expect_tx(bar, HALF_BYTES);
+            // boxes in the order they lie in shared memory: the key tile's halves, then the value tile's
+            tma_load_2d_hint(tiles_u32 + 2 * buf * TILE_BYTES + warp * HALF_BYTES, warp < D / 64 ? &map_k : &map_v,
+                             (warp % (D / 64)) * 64, y, bar, kv_policy);
         }
     };
+    // Waits for the page of a tile pair, a second at most (then the status tells, and the block goes on without waiting
+    // any longer).  All threads wait: each must see the copy's bytes itself.
+    auto wait_page = [&](int buf) {
+        const uint32_t bar = bar0 + 8 * buf, parity = (parity_bits >> buf) & 1u;
+        bool there = mbar_try_wait(bar, parity) != 0;
+        if (!there) {
+            const unsigned long long t0 = global_ns();
+            while (!there) {
+#pragma unroll 1
+                for (int i = 0; i < 64 && !there; i++) there = mbar_try_wait(bar, parity) != 0;
+                if (there) break;
+                if (*reinterpret_cast<volatile int*>(gave_up)) break;
+                if (global_ns() - t0 > PAGE_WAIT_LIMIT_NS) {
+                    if (atomicExch(gave_up, 1) == 0) gfb_report(status, GFB_ERR_WAIT_TIMEOUT, 300 + buf, (int)(blockIdx.x + gridDim.x * blockIdx.y));
+                    break;
+                }
+            }
+        }
+        if (there) {
+            parity_bits ^= 1u << buf;
+            pending_bits &= ~(1u << buf);
+        }
+    };
+    // A block that is its sequence's only slice and has no window starts at the table's first entry whatever the
+    // length is: its entries are then asked for together with the length, not behind it.
+    const bool from_zero = splits == 1 && window <= 0;
+    int ahead[DECODE_NBUF];                      // entries ahead_first .. ahead_first + DECODE_NBUF - 1
+    int ahead_first = -1;
+    auto entries_ahead = [&](int first) {
+        ahead_first = first;
+#pragma unroll
+        for (int a = 0; a < DECODE_NBUF; a++) ahead[a] = entry(first + a);
+    };
+    int next_entry = -1;                         // of page p + DECODE_NBUF - 1 while page p is worked on
     // DECODE_NBUF - 1 pages in flight while q is prepared and, later, while a page is worked on
     auto first_pages = [&]() {
+        if (ahead_first != p0) entries_ahead(p0);
 #pragma unroll
-        for (int a = 0; a < DECODE_NBUF - 1; a++) {
-            if (p0 + a < p1) issue(p0 + a, a);
-            cp_async_commit();
-        }
+        for (int a = 0; a < DECODE_NBUF - 1; a++)
+            if (p0 + a < p1) issue(p0 + a, a, ahead[a]);
+        next_entry = ahead[DECODE_NBUF - 1];
     };
     // Only a kernel that appends may ask for pages this early: it patches its own token's row into the copy of the
     // last page, and all other rows were written in earlier steps.  A kernel that reads what ANOTHER kernel of this
     // step stores (SRC_Q behind the rotary/append kernel; append == 0 behind the cache entry's owner) must not copy
     // a page before that store has landed, so it asks behind the wait.
     const bool early = SRC != SRC_Q && rs.append != 0;        // uniform over the grid
+    constexpr int half = D / 2;
+    constexpr int IT = 8 * half / THREADS;                    // q pairs per thread; one more pair for k or v
+    // (cos, sin) of the token's position for this thread's pairs of q and of k, and the table entry of the page that
+    // takes the new key and value: asked for as soon as a position is known, and again if it was another one
+    float2 csq[IT], csk;
+    int cs_pos = -2, last_entry = -1;
+    auto position_loads = [&]() {
+        cs_pos = pos;
+        const bool in_table = pos >= 0 && pos < rs.table_len;
+        const float* row = rs.table + (size_t)(in_table ? pos : 0) * half * 2;
+#pragma unroll
+        for (int it = 0; it < IT; it++) csq[it] = __ldg(reinterpret_cast<const float2*>(row + 2 * ((tid + it * THREADS) % half)));
+        csk = __ldg(reinterpret_cast<const float2*>(row + 2 * (tid % half)));
+        last_entry = entry(last_page);
+    };
     int len_early = 0;
     if (early) {
+        if (from_zero) entries_ahead(0);
         len_early = __ldcg((rs.lengths_early ? rs.lengths_early : b.lengths) + slot);
         plan(len_early);
         first_pages();
+        position_loads();
     }
     gfb_pdl_wait();
     const int len_now = __ldcg(b.lengths + slot);
@@ -374,18 +514,20 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         len_early = len_now;
         plan(len_now);
         first_pages();
+        if (SRC != SRC_Q) position_loads();
     }
     // SRC != SRC_Q: the new key and value of this token, kept in registers by the threads that made them.  The
     // slice that owns the last page patches them into its shared-memory copy of that page: the page may have
     // been read before the store to the cache landed.
-    constexpr int half = D / 2;
     bool patch = false;
     int off = 0, new_i0 = 0, new_i1 = 1;
     __nv_bfloat16 new0 = __float2bfloat16_rn(0.f), new1 = new0;
     // the length was another one after all: drop what was requested and start again (uniform over the block)
     auto settle_length = [&]() {
         if (len_now != len_early) {
-            cp_async_wait<0>();
+#pragma unroll
+            for (int a = 0; a < DECODE_NBUF - 1; a++)
+                if (pending_bits >> a & 1u) wait_page(a);
             __syncthreads();
             bad_page = false;
             plan(len_now);
@@ -399,7 +541,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         }
         settle_length();
     } else {
-        constexpr int IT = 8 * half / THREADS;                    // q pairs per thread; one more pair for k or v
         const size_t W = (size_t)(H + 2 * G) * D;
         size_t e0[IT + 1], e1[IT + 1];
         int qi0[IT], qi1[IT], qrow[IT], qi[IT];
@@ -429,15 +570,15 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         float x0[IT + 1], x1[IT + 1];
         load_pairs<SRC, IT + 1>(rs, e0, e1, x0, x1);
         settle_length();                                           // from here on the position is certain
+        if (cs_pos != pos) position_loads();
         const bool ok = pos >= 0 && pos < rs.table_len;
         if (!ok && tid == 0 && g == 0 && z == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
-        const float* cs_row = rs.table + (size_t)(ok ? pos : 0) * half * 2;
         const int n_all = last_page - first_page + 1;
         const int z_last = (n_all - 1) / per;
         int page = -1;
         if (rs.append && ok && z == z_last) {
             off = pos - last_page * PAGE;
-            page = last_page < kv.max_pages ? pt[last_page] : -1;
+            page = last_entry;
             if (page < 0 || page >= kv.n_pages) {
                 if (tid == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, t, pos);
                 page = -1;
@@ -446,7 +587,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         patch = page >= 0 && tid < 2 * half;
 #pragma unroll
         for (int it = 0; it < IT; it++) {
-            const float2 cs = *reinterpret_cast<const float2*>(cs_row + 2 * qi[it]);
+            const float2 cs = csq[it];
             const bool live = ok && qrow[it] < rep;
             qs[qrow[it] * PITCH + qi0[it]] = __float2bfloat16_rn(live ? x0[it] * cs.x - x1[it] * cs.y : 0.f);
             qs[qrow[it] * PITCH + qi1[it]] = __float2bfloat16_rn(live ? x1[it] * cs.x + x0[it] * cs.y : 0.f);
@@ -454,7 +595,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         if (patch) {
             const size_t dst = (((size_t)page * G + g) * PAGE + off) * D;
             if (is_key) {                                     // the key: rotated
-                const float2 cs = *reinterpret_cast<const float2*>(cs_row + 2 * ki);
+                const float2 cs = csk;
                 new0 = __float2bfloat16_rn(x0[IT] * cs.x - x1[IT] * cs.y);
                 new1 = __float2bfloat16_rn(x1[IT] * cs.x + x0[IT] * cs.y);
             } else {                                          // the value: copied
@@ -482,20 +623,19 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
 
     for (int p = p0; p < p1; p++) {
         const int buf = (p - p0) % DECODE_NBUF;
-        if (p + DECODE_NBUF - 1 < p1) issue(p + DECODE_NBUF - 1, (p - p0 + DECODE_NBUF - 1) % DECODE_NBUF);
-        cp_async_commit();
-        cp_async_wait<DECODE_NBUF - 1>();
-        __syncthreads();
+        if (p + DECODE_NBUF - 1 < p1) issue(p + DECODE_NBUF - 1, (p - p0 + DECODE_NBUF - 1) % DECODE_NBUF, next_entry);
+        next_entry = entry(p + DECODE_NBUF);                   // in flight while this page is worked on
+        wait_page(buf);
         if (SRC != SRC_Q && p == last_page) {                  // uniform: the block's last page holds the new token
             if (patch) {
-                __nv_bfloat16* row = tiles + (2 * buf + (tid < half ? 0 : 1)) * TILE + off * PITCH;
-                row[new_i0] = new0;
-                row[new_i1] = new1;
+                uint8_t* tile = smem + (2 * buf + (tid < half ? 0 : 1)) * TILE_BYTES;
+                *reinterpret_cast<__nv_bfloat16*>(tile + swz(off, new_i0)) = new0;
+                *reinterpret_cast<__nv_bfloat16*>(tile + swz(off, new_i1)) = new1;
             }
             __syncthreads();
         }
-        const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf) * TILE);
-        const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(tiles + (2 * buf + 1) * TILE);
+        const uint32_t kbase = tiles_u32 + 2 * buf * TILE_BYTES;
+        const uint32_t vbase = kbase + TILE_BYTES;
 
         // scores of this warp's 16 keys (two n-tiles of 8) for rows = heads
         float sc[2][4];
@@ -504,7 +644,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
 #pragma unroll
         for (int k = 0; k < KSTEPS; k++) {
             // matrices: (keys 0-7, dims lo), (keys 0-7, dims hi), (keys 8-15, dims lo), (keys 8-15, dims hi)
-            uint32_t addr = kbase + (uint32_t)(((warp * 16 + (mid >> 1) * 8 + mr) * PITCH + k * 16 + (mid & 1) * 8) * 2);
+            uint32_t addr = kbase + swz(warp * 16 + (mid >> 1) * 8 + mr, k * 16 + (mid & 1) * 8);
             uint32_t b0, b1, b2, b3;
             ldsm_x4(addr, b0, b1, b2, b3);
             mma_rows8(sc[0], qa[k][0], qa[k][1], b0, b1);
@@ -541,7 +681,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         for (int j = 0; j < NT; j += 2) {
             o[j][0] *= corr; o[j][1] *= corr; o[j + 1][0] *= corr; o[j + 1][1] *= corr;
             // matrices: (keys 0-7, dims j), (keys 8-15, dims j), (keys 0-7, dims j+1), (keys 8-15, dims j+1)
-            uint32_t addr = vbase + (uint32_t)(((warp * 16 + (mid & 1) * 8 + mr) * PITCH + (j + (mid >> 1)) * 8) * 2);
+            uint32_t addr = vbase + swz(warp * 16 + (mid & 1) * 8 + mr, (j + (mid >> 1)) * 8);
             uint32_t b0, b1, b2, b3;
             ldsm_x4_trans(addr, b0, b1, b2, b3);
             mma_rows8(o[j], pa0, pa2, b0, b1);
@@ -549,44 +689,54 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __res
         }
         __syncthreads();                                       // this buffer is refilled next round
     }
-    cp_async_wait<0>();
-    __syncthreads();
+    if (pending_bits) {                                        // only after a wait that ran out: once more, then leave
+#pragma unroll
+        for (int a = 0; a < DECODE_NBUF; a++)
+            if (pending_bits >> a & 1u) wait_page(a);
+    }
     if (bad_page && tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, bad_index);
 
-    // merge the four warps' partial softmaxes; the tile area is free now
-    float* Ow = (float*)smem;                                  // [4][8][D]
-    float* mw = Ow + 4 * 8 * D;                                // [4][8]
+    // Merge of the four warps' partial softmaxes; the tile area is free now.  The warps exchange (max, sum) first, each
+    // scales its own sums in registers to the common maximum (and, with one slice, by 1 / the whole sum), and the block
+    // adds the four scaled copies.
+    constexpr int OP = D + 8;                                  // floats per row: the rows of a store fall on different banks
+    float* Ow = (float*)smem;                                  // [4][8][OP]
+    float* mw = Ow + 4 * 8 * OP;                               // [4][8]
     float* lw = mw + 32;                                       // [4][8]
-#pragma unroll
-    for (int j = 0; j < NT; j++) {
-        Ow[(warp * 8 + gq) * D + j * 8 + 2 * t4] = o[j][0];
-        Ow[(warp * 8 + gq) * D + j * 8 + 2 * t4 + 1] = o[j][1];
-    }
     if (t4 == 0) { mw[warp * 8 + gq] = m_run; lw[warp * 8 + gq] = l_run; }
     __syncthreads();
-    for (int idx = tid; idx < rep * D; idx += THREADS) {
-        const int h = idx / D, dim = idx - h * D;
-        float m = fmaxf(fmaxf(mw[h], mw[8 + h]), fmaxf(mw[16 + h], mw[24 + h]));
-        float l = 0.f, acc = 0.f;
+    const float m_all = fmaxf(fmaxf(mw[gq], mw[8 + gq]), fmaxf(mw[16 + gq], mw[24 + gq]));
+    float l_all = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
-            float mm = mw[w * 8 + h];
-            if (mm == -INFINITY) continue;
-            float f = exp2f(mm - m);
-            l += lw[w * 8 + h] * f;
-            acc += Ow[(w * 8 + h) * D + dim] * f;
+    for (int w = 0; w < 4; w++) {
+        const float mm = mw[w * 8 + gq];
+        if (mm != -INFINITY) l_all += lw[w * 8 + gq] * exp2f(mm - m_all);
+    }
+    float f = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_all);
+    if (splits == 1) f = l_all > 0.f ? f / l_all : 0.f;
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+        *reinterpret_cast<float2*>(Ow + (warp * 8 + gq) * OP + j * 8 + 2 * t4) = make_float2(o[j][0] * f, o[j][1] * f);
+    if (splits > 1 && warp == 0 && t4 == 0 && gq < rep) {
+        float* ml = scratch_ml + (((size_t)t * H + g * rep + gq) * splits + z) * 2;
+        ml[0] = m_all;
+        ml[1] = l_all;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rep * (D / 2); idx += THREADS) {
+        const int h = idx / (D / 2), dim = 2 * (idx - h * (D / 2));
+        float2 acc = *reinterpret_cast<const float2*>(Ow + h * OP + dim);
+#pragma unroll
+        for (int w = 1; w < 4; w++) {
+            const float2 a = *reinterpret_cast<const float2*>(Ow + (w * 8 + h) * OP + dim);
+            acc.x += a.x;
+            acc.y += a.y;
         }
         const int head = g * rep + h;
-        if (splits == 1) {
-            out[((size_t)t * H + head) * D + dim] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-        } else {
-            scratch_o[(((size_t)t * H + head) * splits + z) * D + dim] = acc;
-            if (dim == 0) {
-                float* ml = scratch_ml + (((size_t)t * H + head) * splits + z) * 2;
-                ml[0] = m;
-                ml[1] = l;
-            }
-        }
+        if (splits == 1)
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * H + head) * D + dim) = __floats2bfloat162_rn(acc.x, acc.y);
+        else
+            *reinterpret_cast<float2*>(scratch_o + (((size_t)t * H + head) * splits + z) * D + dim) = acc;
     }
 }
 
@@ -611,17 +761,33 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const f
     }
 }
 
-// Launch of the tensor-core decode kernel for head_dim 64 or 128 and one of the three sources: 4 padded tiles
-// + the query rows of shared memory; the merge area reuses the tiles.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Launch of the tensor-core decode kernel for head_dim 64 or 128 and one of the three sources: the tile pairs, the
+// query rows and the barriers of shared memory; the merge area reuses the tiles.
 cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, const void* q, void* out, float* so, float* sml,
                               GfbPagedKV kv, GfbBatch b, int H, int G, float scale, int window, int splits, int* status,
                               RopeSource rs, int pages_per_slice) {
-    typedef void (*Kern)(const __nv_bfloat16*, __nv_bfloat16*, float*, float*, GfbPagedKV, GfbBatch, int, int, float, int, int,
-                         int*, RopeSource);
+    typedef void (*Kern)(const CUtensorMap, const CUtensorMap, const __nv_bfloat16*, __nv_bfloat16*, float*, float*, GfbPagedKV,
+                         GfbBatch, int, int, float, int, int, int*, RopeSource);
     // Tile pairs per block: five where the grid leaves at most one block per SM anyway (a short context is then
-    // requested all at once); two where there are several rounds of short blocks (a few pages each: three blocks
-    // fit an SM and their set-ups and merges overlap: 13B sizes at batch 32, 50 -> 42 us); three otherwise (long
-    // slices want two pages in flight behind the one being worked on).
+    // requested all at once); two where more than three blocks per SM wait with a few pages each (three blocks then fit
+    // an SM and their set-ups and merges overlap: 40 heads of their own keys at batch 32, 42 -> 38 us; 8 groups at
+    // batch 64 and 150 tokens, 14.5 -> 12.6 us); three otherwise (long slices want two pages in flight behind the one
+    // being worked on).
     static const Kern kerns[3][2][3] = {
         {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_MANY>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_MANY>,
           attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_MANY>},
@@ -643,9 +809,30 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
     }
     const int di = d == 128 ? 1 : 0;
     const long blocks = (long)grid.x * grid.y * grid.z;
-    const int few = blocks <= sms ? 1 : (blocks >= 4L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
+    const int few = blocks <= sms ? 1 : (blocks > 3L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
     const int nbuf = few == 1 ? DECODE_NBUF_FEW : few == 2 ? DECODE_NBUF_SHORT : DECODE_NBUF_MANY;
-    const size_t msmem = (size_t)(2 * nbuf * PAGE + 8) * (d + 8) * 2;
+    // alignment slack, tiles, q rows, barriers and a flag
+    const size_t msmem = 1024 + (size_t)2 * nbuf * PAGE * d * 2 + (size_t)8 * (d + 8) * 2 + 8 * nbuf + 16;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) {
+        gfb_fail("decode attention: the driver does not export cuTensorMapEncodeTiled");
+        return cudaErrorInvalidValue;
+    }
+    CUtensorMap mk, mv;
+    for (int i = 0; i < 2; i++) {                            // a pool seen as [pages x heads x 64 rows][d]
+        cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)kv.n_pages * G * PAGE};
+        cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)PAGE};
+        cuuint32_t es[2] = {1, 1};
+        CUresult r = enc(i ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(i ? kv.v_pool : kv.k_pool), dims,
+                         strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            gfb_fail("decode attention: tensor map of the cache refused (%d): %d pages, %d heads, head_dim %d, pool at %p",
+                     (int)r, kv.n_pages, G, d, i ? kv.v_pool : kv.k_pool);
+            return cudaErrorInvalidValue;
+        }
+    }
     Kern kern = kerns[few][di][src];
     if (msmem > 48 * 1024 && !configured[few][di][src]) {
         cudaError_t a = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem);
@@ -656,7 +843,7 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
         configured[few][di][src] = true;
     }
     gfb_error_text[0] = 0;
-    return gfb_launch(kern, grid, dim3(THREADS), msmem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b,
+    return gfb_launch(kern, grid, dim3(THREADS), msmem, stream, mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, so, sml, kv, b,
                       H, G, scale * 1.4426950408889634f, window, splits, status, rs);
 }
 
@@ -713,7 +900,8 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
 // With append = 0 only q is taken from it (the layer reads a cache that another layer wrote).
 // The kernel asks for its first pages before the preceding kernel has ended, on the lengths as they are then, and
 // reads the lengths again afterwards; lengths_early (optional, per slot like lengths) stands in for the first read,
-// which lets a test make the two differ.  max_kv_len (0: unknown): the longest sequence of the batch after this step,
+// which lets a test make the two differ.  Every sequence brings at most one token (a second one would attend to a key
+// that this launch has not stored yet).  max_kv_len (0: unknown): the longest sequence of the batch after this step,
 // as the host knows it; it only chooses how many pages a block keeps in flight.
 GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k_pool, void* v_pool, const int* page_table,
                                  int max_pages, int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq,
@@ -728,11 +916,13 @@ GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k
     if (splits < 1 || G > 65535 || splits > 65535) return gfb_fail("gfb_attn_decode_rope: bad split count %d", splits);
     if (splits > 1 && scratch == nullptr) return gfb_fail("gfb_attn_decode_rope: %d slices need scratch memory", splits);
     if (pairing != 0 && pairing != 1) return gfb_fail("gfb_attn_decode_rope: unknown pairing %d", pairing);
+    if ((uintptr_t)src % 8) return gfb_fail("gfb_attn_decode_rope: the q/k/v product must start on an 8-byte boundary");
     GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     float* so = scratch;
     float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
-    RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append, lengths_early};
+    RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append, lengths_early,
+                  n_tokens == n_seqs ? 1 : 0};
     const int pages = max_kv_len > 0 ? (max_kv_len + PAGE - 1) / PAGE : 0;
     cudaError_t e = launch_decode_mma(d, n_part > 0 ? SRC_PARTIALS : SRC_QKV, dim3(n_tokens, G, splits), stream, nullptr, out, so, sml,
                                       kv, b, H, G, scale, window, splits, status, rs, (pages + splits - 1) / splits);
