@@ -235,16 +235,18 @@ def test_fused_decode_attention_sees_the_new_token_and_a_far_key():
         torch.testing.assert_close(out[1, h * d:(h + 1) * d].float(), v_pool[far_page, h // (H // G), 9].float(), rtol=2e-2, atol=2e-2)
 
 
-def test_decode_attention_of_a_large_batch():
-    """64 sequences at scattered positions (several blocks per SM): the fused and the plain entry of the decode
-    kernel against the plain implementation."""
+@pytest.mark.parametrize("stride,n", [(37, 64), (211, 64), (37, 20)])
+def test_decode_attention_of_a_large_batch(stride, n):
+    """Many sequences at scattered positions: the fused and the plain entry of the decode kernel against the plain
+    implementation.  The three cases run the kernel's three buffer depths: more than three blocks per SM with few
+    pages each (two tile pairs), with many pages (three), and a grid within one block per SM (five)."""
     H, G, d = 32, 8, 128
-    n = 64
-    starts = [(37 * i) % 300 for i in range(n)]
-    batch, table, n_pages = make_batch([1] * n, starts, n + 3, 64, 8, seed=5)
+    starts = [(stride * i) % (8 * stride) for i in range(n)]
+    pages = max(starts) // 64 + 2
+    batch, table, n_pages = make_batch([1] * n, starts, n + 3, 64, pages, seed=5)
     dt = torch.bfloat16
     W = (H + 2 * G) * d
-    rt = torch.empty(8 * 64, d // 2, 2, device=DEV)
+    rt = torch.empty(pages * 64, d // 2, 2, device=DEV)
     ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).to(DEV), rt)
     k0, v0 = rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5)
     kv, kv_ref = PagedKV(k0.clone(), v0.clone(), table, 64), PagedKV(k0.clone(), v0.clone(), table, 64)
@@ -261,3 +263,36 @@ def test_decode_attention_of_a_large_batch():
     out2 = torch.empty_like(out)
     ops.kernels()._attention_bf16(q_ref, kv_ref, batch, out2, H, G, d, scale, None, splits=1)
     torch.testing.assert_close(out2.float(), ref.float(), rtol=2e-2, atol=1e-2)
+
+
+def test_fused_decode_attention_with_a_sequence_that_brings_no_token():
+    """Token t is sequence t only while every sequence brings a token; with one that brings none the kernel has to
+    look the sequence up (its other way of indexing), and the result is that of the same tokens without that
+    sequence in the batch."""
+    H, G, d = 8, 2, 128
+    starts = [70, 500, 3, 129]
+    dt = torch.bfloat16
+    W = (H + 2 * G) * d
+    rt = torch.empty(10 * 64, d // 2, 2, device=DEV)
+    ops.rope_table((1.0 / (10000 ** (torch.arange(d // 2).float() * 2 / d))).to(DEV), rt)
+    scale = 1 / math.sqrt(d)
+    outs = []
+    for q_lens in ([1, 0, 1, 1], [1, 1, 1, 1]):
+        batch, table, n_pages = make_batch(q_lens, starts, 6, 64, 10, seed=2)
+        T = batch.n_tokens
+        k0, v0 = rnd(n_pages, G, 64, d, dtype=dt, seed=4), rnd(n_pages, G, 64, d, dtype=dt, seed=5)
+        kv = PagedKV(k0.clone(), v0.clone(), table, 64)
+        rows = [i for i, q in enumerate(q_lens) if q]
+        qkv = rnd(4, W, dtype=dt, seed=1)[rows].contiguous()
+        out = torch.empty(T, H * d, dtype=dt, device=DEV)
+        assert ops.kernels().rope_append_attention(qkv, None, kv, batch, rt, out, H, G, d, "interleaved", True, scale, None)
+        ops.check_status(batch.status)
+        if len(rows) < 4:
+            kv_ref, ref, q_ref = PagedKV(k0.clone(), v0.clone(), table, 64), torch.empty_like(out), torch.empty(T, H, d, dtype=dt, device=DEV)
+            REF.rope_append(qkv, q_ref, kv_ref, batch, rt, H, G, d, "interleaved", True, None)
+            REF.attention(q_ref, kv_ref, batch, ref, H, G, d, scale, None)
+            torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
+            torch.testing.assert_close(kv.k_pool.float(), kv_ref.k_pool.float(), rtol=2e-2, atol=2e-2)
+        outs.append((rows, out))
+    (rows_a, a), (rows_b, b) = outs
+    assert torch.equal(a, b[rows_a])                      # the same pages and tokens: bit for bit the same rows
