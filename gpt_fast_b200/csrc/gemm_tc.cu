@@ -153,6 +153,51 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// The columns of an epilogue round with one instruction and one wait (four loads of sixteen in flight together made
+// the compiler spill).
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {"
+        "%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16_raw(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld32_raw(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {"
+        "%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void tmem_ld_group(uint32_t taddr, uint32_t (&r)[N]);
+template <> __device__ __forceinline__ void tmem_ld_group<16>(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16_raw(taddr, r); }
+template <> __device__ __forceinline__ void tmem_ld_group<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32_raw(taddr, r); }
+template <> __device__ __forceinline__ void tmem_ld_group<64>(uint32_t taddr, uint32_t (&r)[64]) { tmem_ld64(taddr, r); }
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -360,21 +405,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     epilogue_rows<BN, EPI == EPI_PARTIAL ? EPI_STORE : EPI, TO>(reinterpret_cast<float*>(aligned), taddr, q, lane,
                                                                                 out, row0, col0, R, Cc, ldo);
             } else {
+            // Up to 64 accumulator columns (tokens) a round, brought from tensor memory by one load.
+            constexpr int GROUP = BN < 64 ? BN : 64;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
+            for (int c = 0; c < BN; c += GROUP) {
                 if (col0 + c >= Cc) break;                  // uniform: nothing left in this tile
-                float v[16];
-                tmem_ld16(taddr + c, v);
-                {
+                uint32_t raw[GROUP];
+                tmem_ld_group<GROUP>(taddr + c, raw);
+                if (EPI == EPI_SWIGLU) {
+                    // Rows 2i (gate) and 2i + 1 (up) sit in neighbouring lanes; the even lane finishes the even
+                    // tokens of the pair and the odd lane the odd ones, so each lane does half of the work.
+                    const int p = lane & 1;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        int m = col0 + c + j;               // token
-                        float x = v[j];
-                        if (EPI == EPI_SWIGLU) {
-                            float other = __shfl_xor_sync(0xffffffffu, x, 1);
-                            if (m < Cc && r < R && !(lane & 1))
-                                ((__nv_bfloat16*)out)[(size_t)m * ldo + (r >> 1)] = __float2bfloat16_rn(silu_mul(x, other));
-                        } else if (m < Cc && r < R) {
+                    for (int j = 0; j < GROUP; j += 2) {
+                        const float lo = __uint_as_float(raw[j]), hi = __uint_as_float(raw[j + 1]);
+                        const float mine = p ? hi : lo;
+                        const float theirs = __shfl_xor_sync(0xffffffffu, p ? lo : hi, 1);
+                        const int m = col0 + c + j + p;     // token
+                        if (m < Cc && r < R)
+                            ((__nv_bfloat16*)out)[(size_t)m * ldo + (r >> 1)] =
+                                __float2bfloat16_rn(p ? silu_mul(theirs, mine) : silu_mul(mine, theirs));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < GROUP; j++) {
+                        const int m = col0 + c + j;         // token
+                        const float x = __uint_as_float(raw[j]);
+                        if (m < Cc && r < R) {
                             if (EPI == EPI_PARTIAL) partial[((size_t)blockIdx.z * Cc + m) * R + r] = x;
                             else if (EPI == EPI_ADD) ((float*)out)[(size_t)m * ldo + r] += x;
                             else if (sizeof(TO) == 4) ((float*)out)[(size_t)m * ldo + r] = x;
