@@ -198,6 +198,19 @@ template <> __device__ __forceinline__ void tmem_ld_group<16>(uint32_t taddr, ui
 template <> __device__ __forceinline__ void tmem_ld_group<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32_raw(taddr, r); }
 template <> __device__ __forceinline__ void tmem_ld_group<64>(uint32_t taddr, uint32_t (&r)[64]) { tmem_ld64(taddr, r); }
 
+// Barrier number 1 for the four epilogue warps (128 threads), alone or with the AND of a flag over them.
+__device__ __forceinline__ void epilogue_warps_sync() { asm volatile("barrier.cta.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ bool epilogue_warps_all(bool flag) {
+    uint32_t all;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(all) : "r"((uint32_t)flag) : "memory");
+    return all != 0;
+}
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -398,15 +411,75 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int r = row0 + q * 32 + lane;
         bool ok = mbar_wait(smem_u32(&bars->accum), 0, abort_flag, status, 3);
         tc_fence_after();
-        if (ok) {
+        {
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
             if constexpr (!SWAP) {
-                if (row0 + q * 32 < R)
+                if (ok && row0 + q * 32 < R)
                     epilogue_rows<BN, EPI == EPI_PARTIAL ? EPI_STORE : EPI, TO>(reinterpret_cast<float*>(aligned), taddr, q, lane,
                                                                                 out, row0, col0, R, Cc, ldo);
             } else {
             // Up to 64 accumulator columns (tokens) a round, brought from tensor memory by one load.
             constexpr int GROUP = BN < 64 ? BN : 64;
+            // From 32 tokens on the tile goes through shared memory (the ring is free by now): a thread owns one weight
+            // row, so its direct stores are 4 bytes each, 128 per warp and token, and 64 of them per thread kept a
+            // block for 3 us; from the staged tile a warp writes a token's 128 rows with one 16-byte store per lane.
+            const int ldv = EPI == EPI_PARTIAL ? R : ldo;
+            const bool staged = BN >= 32 && R % 4 == 0 && ldv % (EPI == EPI_SWIGLU ? 2 : 4) == 0;   // uniform over the grid
+            if (staged) {
+                float* tile = reinterpret_cast<float*>(aligned);        // [tokens][128 rows]
+                const bool all_ok = epilogue_warps_all(ok);             // all four warps or none
+                if (all_ok) {
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += GROUP) {
+                        if (col0 + c >= Cc) break;                      // uniform: nothing left in this tile
+                        uint32_t raw[GROUP];
+                        tmem_ld_group<GROUP>(taddr + c, raw);
+#pragma unroll
+                        for (int j = 0; j < GROUP; j++) tile[(c + j) * BM + q * 32 + lane] = __uint_as_float(raw[j]);
+                    }
+                    epilogue_warps_sync();
+                    const int n_tok = min(BN, Cc - col0);
+                    const int rr = row0 + 4 * lane;                     // this lane's four rows of every token
+#pragma unroll 2
+                    for (int j = q; j < n_tok; j += 4) {
+                        const int m = col0 + j;
+                        const float4 v = *reinterpret_cast<const float4*>(tile + j * BM + 4 * lane);
+                        const float e[4] = {v.x, v.y, v.z, v.w};
+                        if (rr + 3 < R) {
+                            if (EPI == EPI_SWIGLU) {
+                                *reinterpret_cast<uint32_t*>((__nv_bfloat16*)out + (size_t)m * ldo + (rr >> 1)) =
+                                    pack_bf16(silu_mul(v.x, v.y), silu_mul(v.z, v.w));
+                            } else if (EPI == EPI_PARTIAL) {
+                                *reinterpret_cast<float4*>(partial + ((size_t)blockIdx.z * Cc + m) * R + rr) = v;
+                            } else if (EPI == EPI_ADD) {
+                                float4* dst = reinterpret_cast<float4*>((float*)out + (size_t)m * ldo + rr);
+                                float4 a = *dst;
+                                a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+                                *dst = a;
+                            } else if (sizeof(TO) == 4) {
+                                *reinterpret_cast<float4*>((float*)out + (size_t)m * ldo + rr) = v;
+                            } else {
+                                uint2 pk;
+                                pk.x = pack_bf16(v.x, v.y);
+                                pk.y = pack_bf16(v.z, v.w);
+                                *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)m * ldo + rr) = pk;
+                            }
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int r1 = rr + u;
+                                if (r1 >= R) break;
+                                if (EPI == EPI_SWIGLU) {
+                                    if (!(u & 1)) ((__nv_bfloat16*)out)[(size_t)m * ldo + (r1 >> 1)] = __float2bfloat16_rn(silu_mul(e[u], e[u + 1]));
+                                } else if (EPI == EPI_PARTIAL) partial[((size_t)blockIdx.z * Cc + m) * R + r1] = e[u];
+                                else if (EPI == EPI_ADD) ((float*)out)[(size_t)m * ldo + r1] += e[u];
+                                else if (sizeof(TO) == 4) ((float*)out)[(size_t)m * ldo + r1] = e[u];
+                                else ((__nv_bfloat16*)out)[(size_t)m * ldo + r1] = __float2bfloat16_rn(e[u]);
+                            }
+                        }
+                    }
+                }
+            } else if (ok) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += GROUP) {
                 if (col0 + c >= Cc) break;                  // uniform: nothing left in this tile
@@ -439,6 +512,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         }
                     }
                 }
+            }
             }
             }
         }
