@@ -24,7 +24,7 @@ constexpr int THREADS = 128;
 constexpr int MAX_REP = 8;          // query heads per key/value head
 constexpr int MAX_DPT = 2;          // head_dim <= THREADS * MAX_DPT
 // K/V tile pairs of the tensor-core decode kernel: NBUF - 1 pages are in flight per block.  3 lets two blocks share
-// an SM and 2 three; 5 (one block per SM) is for small grids, where a short context is then requested all at once.
+// an SM and 2 three; 5 (one block per SM) is for the smallest grids, where a short context is then requested all at once.
 constexpr int DECODE_NBUF_MANY = 3, DECODE_NBUF_FEW = 5, DECODE_NBUF_SHORT = 2;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -783,11 +783,12 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
                               RopeSource rs, int pages_per_slice) {
     typedef void (*Kern)(const CUtensorMap, const CUtensorMap, const __nv_bfloat16*, __nv_bfloat16*, float*, float*, GfbPagedKV,
                          GfbBatch, int, int, float, int, int, int*, RopeSource);
-    // Tile pairs per block: five where the grid leaves at most one block per SM anyway (a short context is then
-    // requested all at once); two where more than three blocks per SM wait with a few pages each (three blocks then fit
-    // an SM and their set-ups and merges overlap: 40 heads of their own keys at batch 32, 42 -> 38 us; 8 groups at
-    // batch 64 and 150 tokens, 14.5 -> 12.6 us); three otherwise (long slices want two pages in flight behind the one
-    // being worked on).
+    // Tile pairs per block: five where the grid covers at most a quarter of the SMs (a short context is then requested
+    // all at once; with more blocks than that, one block of five pairs per SM leaves no room for the blocks of the
+    // product behind it, which want to fetch their weights meanwhile: 8 sequences x 8 heads, 2.99 -> 2.92 ms per step);
+    // two where more than three blocks per SM wait with a few pages each (three blocks then fit an SM and their
+    // set-ups and merges overlap: 40 heads of their own keys at batch 32, 42 -> 38 us; 8 groups at batch 64 and 150
+    // tokens, 14.5 -> 12.6 us); three otherwise (long slices want two pages in flight behind the one being worked on).
     static const Kern kerns[3][2][3] = {
         {{attn_decode_mma_kernel<64, SRC_Q, DECODE_NBUF_MANY>, attn_decode_mma_kernel<64, SRC_QKV, DECODE_NBUF_MANY>,
           attn_decode_mma_kernel<64, SRC_PARTIALS, DECODE_NBUF_MANY>},
@@ -809,7 +810,7 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
     }
     const int di = d == 128 ? 1 : 0;
     const long blocks = (long)grid.x * grid.y * grid.z;
-    const int few = blocks <= sms ? 1 : (blocks > 3L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
+    const int few = blocks <= sms / 4 ? 1 : (blocks > 3L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
     const int nbuf = few == 1 ? DECODE_NBUF_FEW : few == 2 ? DECODE_NBUF_SHORT : DECODE_NBUF_MANY;
     // alignment slack, tiles, q rows, barriers and a flag
     const size_t msmem = 1024 + (size_t)2 * nbuf * PAGE * d * 2 + (size_t)8 * (d + 8) * 2 + 8 * nbuf + 16;
