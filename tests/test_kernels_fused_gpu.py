@@ -235,11 +235,12 @@ def test_fused_decode_attention_sees_the_new_token_and_a_far_key():
         torch.testing.assert_close(out[1, h * d:(h + 1) * d].float(), v_pool[far_page, h // (H // G), 9].float(), rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("stride,n", [(37, 64), (211, 64), (37, 20)])
+@pytest.mark.parametrize("stride,n", [(37, 64), (211, 64), (37, 20), (37, 4)])
 def test_decode_attention_of_a_large_batch(stride, n):
     """Many sequences at scattered positions: the fused and the plain entry of the decode kernel against the plain
-    implementation.  The three cases run the kernel's three buffer depths: more than three blocks per SM with few
-    pages each (two tile pairs), with many pages (three), and a grid within one block per SM (five)."""
+    implementation.  The cases run the kernel's three buffer depths: more than three blocks per SM with few pages
+    each (two tile pairs), with many pages or a grid of about one block per SM (three), and a grid on a quarter of
+    the SMs (five)."""
     H, G, d = 32, 8, 128
     starts = [(stride * i) % (8 * stride) for i in range(n)]
     pages = max(starts) // 64 + 2
