@@ -819,6 +819,11 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
         gfb_fail("decode attention: the driver does not export cuTensorMapEncodeTiled");
         return cudaErrorInvalidValue;
     }
+    if ((long long)kv.n_pages * G * PAGE > 2147483647LL) {       // TMA coordinates are 32-bit
+        gfb_fail("decode attention: %d pages x %d heads x %d tokens do not fit the 32-bit row coordinate of a tensor map",
+                 kv.n_pages, G, PAGE);
+        return cudaErrorInvalidValue;
+    }
     CUtensorMap mk, mv;
     for (int i = 0; i < 2; i++) {                            // a pool seen as [pages x heads x 64 rows][d]
         cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)kv.n_pages * G * PAGE};

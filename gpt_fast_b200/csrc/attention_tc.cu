@@ -989,6 +989,9 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return gfb_fail("gfb_attn_prefill_tc: tensor map of q refused (%d)", (int)r);
     }
+    if ((long long)n_pages * G * PAGE > 2147483647LL)           // TMA coordinates are 32-bit
+        return gfb_fail("gfb_attn_prefill_tc: %d pages x %d heads x %d tokens do not fit the 32-bit row coordinate of a tensor map",
+                        n_pages, G, PAGE);
     for (int i = 0; i < 2; i++) {
         cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)n_pages * G * PAGE};
         cuuint64_t strides[1] = {(cuuint64_t)d * 2};
