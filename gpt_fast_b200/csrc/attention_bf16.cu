@@ -269,12 +269,10 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint3
 // c += a * b with rows 8..15 of a equal to zero (a1 = a3 = 0): only c[0], c[1] (rows 0..7) live on, the other two
 // results are zero and are dropped
 __device__ __forceinline__ void mma_rows8(float* c, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    float z2, z3;
+    [[maybe_unused]] float z2, z3;
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %10};"
                  : "+f"(c[0]), "+f"(c[1]), "=f"(z2), "=f"(z3)
                  : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
-    (void)z2;
-    (void)z3;
 }
 
 // Byte offset of element (row, col) in a tile of [64 rows][D] brought as D / 64 boxes with 128-byte swizzle: box
