@@ -864,20 +864,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
     gfb_pdl_launch();
-    gfb_pdl_wait();
+    if (!(warp == 0 && lane == 0)) gfb_pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
             const int total = my_tiles * nkb;
+            // Weights are written by no kernel: the weight halves of the first round of the ring are asked for ahead
+            // of the wait for the preceding kernel (fresh barriers: every stage is free), the activations behind it.
+            const int n_pre = min(stages, total);
+            {
+                int kb = 0, tile = pair;
+                for (int it = 0; it < n_pre; it++) {
+                    const uint32_t full = smem_u32(&bars->full[it]) & PEER_MASK;
+                    if (leader) mbar_expect_tx(smem_u32(&bars->full[it]), 2 * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(ys + it * X_TILE_BYTES, &map_y, kb * BK, (tile / row_tiles) * 256 + (int)rank * 128, full);
+                    if (++kb == nkb) { kb = 0; tile += n_pairs; }
+                }
+            }
+            gfb_pdl_wait();
             int kb = 0, tile = pair, s = 0;
             uint32_t ph = 0;
             int row0 = (tile % row_tiles) * 256 + (int)rank * 128, wrow0 = (tile / row_tiles) * 256 + (int)rank * 128;
             for (int it = 0; it < total; it++) {
-                if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
                 const uint32_t full = smem_u32(&bars->full[s]) & PEER_MASK;        // the leader's barrier
-                if (leader) mbar_expect_tx(smem_u32(&bars->full[s]), 2 * PAIR_STAGE_BYTES);
+                if (it >= n_pre) {
+                    if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag, status, 1)) break;
+                    if (leader) mbar_expect_tx(smem_u32(&bars->full[s]), 2 * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(ys + s * X_TILE_BYTES, &map_y, kb * BK, wrow0, full);
+                }
                 tma_load_2d_pair(xs + s * X_TILE_BYTES, &map_x, kb * BK, row0, full);
-                tma_load_2d_pair(ys + s * X_TILE_BYTES, &map_y, kb * BK, wrow0, full);
                 if (++s == stages) { s = 0; ph ^= 1u; }
                 if (++kb == nkb) {
                     kb = 0;
