@@ -555,30 +555,39 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// drain PCW accumulator columns [c0, c0+PCW) of this warp's 32 rows and apply the epilogue
+// Add-into-residual: a chunk's residual values (32 rows x PCW columns, 8 loads of 16 bytes per lane).  The caller asks
+// for the NEXT chunk's values before it drains a chunk, so that they travel meanwhile.  (The epilogue of a tile stays
+// bound by memory all the same: at a block's last tile all blocks read and write their part of the 32-bit residual
+// at once, 128 KB each way per block in 8 to 9 us.)
+constexpr int RES_LPR = PCW / 4, RES_RPI = 32 / RES_LPR, RES_N = 32 / RES_RPI;
+template <typename TO>
+__device__ __forceinline__ void load_residual_chunk(float4 (&res)[RES_N], int c0, int lane, const TO* out, int grow0, int gcol0,
+                                                    int rows, int N, int ldo) {
+    const int sub = lane / RES_LPR, col = (lane % RES_LPR) * 4;
+#pragma unroll
+    for (int u = 0; u < RES_N; u++) {
+        const int r = RES_RPI * u + sub;
+        res[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows && gcol0 + c0 + col < N)
+            res[u] = *reinterpret_cast<const float4*>((const float*)out + (size_t)(grow0 + r) * ldo + gcol0 + c0 + col);
+    }
+}
+
+// drain PCW accumulator columns [c0, c0+PCW) of this warp's 32 rows and apply the epilogue (res: the chunk's residual
+// values for add-into-residual, unused otherwise)
 template <int EPI, typename TO>
 __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0, int lane, TO* out, int grow0, int gcol0,
-                                            int rows, int N, int ldo) {
+                                            int rows, int N, int ldo, const float4 (&res)[RES_N]) {
     float* mine = stage + lane * PSP;
-    // add-into-residual: the chunk's residual values (32 rows x PCW columns, 8 loads of 16 bytes per lane) are
-    // requested first, so that they travel while the accumulator comes out of tensor memory
-    constexpr int ALPR = PCW / 4, ARPI = 32 / ALPR, ANL = 32 / ARPI;
-    float4 res[ANL];
-    if (EPI == EPI_ADD) {
-        const int sub = lane / ALPR, col = (lane % ALPR) * 4;
+    constexpr int ALPR = RES_LPR, ARPI = RES_RPI, ANL = RES_N;
+    {
+        static_assert(PCW == 32, "one 32-column load from tensor memory per chunk");
+        uint32_t raw[32];
+        tmem_ld32_raw(taddr + c0, raw);
 #pragma unroll
-        for (int u = 0; u < ANL; u++) {
-            const int r = ARPI * u + sub;
-            if (r < rows && gcol0 + c0 + col < N)
-                res[u] = *reinterpret_cast<const float4*>((float*)out + (size_t)(grow0 + r) * ldo + gcol0 + c0 + col);
-        }
-    }
-#pragma unroll
-    for (int c = 0; c < PCW; c += 16) {
-        float v[16];
-        tmem_ld16(taddr + c0 + c, v);
-#pragma unroll
-        for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(mine + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(mine + j) = make_float4(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1]),
+                                                               __uint_as_float(raw[j + 2]), __uint_as_float(raw[j + 3]));
     }
     __syncwarp();
     const int gc = gcol0 + c0;
@@ -752,11 +761,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             tc_fence_after();
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * PBN);
             const int rows = min(32, R - (row0 + q * 32));
+            float4 res[RES_N], res_next[RES_N];
+            if (EPI == EPI_ADD) load_residual_chunk(res, 0, lane, out, row0 + q * 32, col0, rows, Cc, ldo);
 #pragma unroll 1
             for (int c0 = 0; c0 < PBN; c0 += PCW) {
                 if (col0 + c0 >= Cc) break;
-                if (rows > 0) drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo);
+                if (EPI == EPI_ADD) load_residual_chunk(res_next, c0 + PCW, lane, out, row0 + q * 32, col0, c0 + PCW < PBN ? rows : 0, Cc, ldo);
+                if (rows > 0) drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo, res);
                 else { float v[16]; for (int c = 0; c < PCW; c += 16) tmem_ld16(taddr + c0 + c, v); }
+                if (EPI == EPI_ADD) {
+#pragma unroll
+                    for (int u = 0; u < RES_N; u++) res[u] = res_next[u];
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -939,10 +955,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             tc_fence_after();
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * 256);
             const int rows = min(32, R - (row0 + q * 32));
+            float4 res[RES_N], res_next[RES_N];
+            if (EPI == EPI_ADD) load_residual_chunk(res, 0, lane, out, row0 + q * 32, col0, rows, Cc, ldo);
 #pragma unroll 1
             for (int c0 = 0; c0 < 256; c0 += PCW) {
                 if (col0 + c0 >= Cc || rows <= 0) break;
-                drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo);
+                if (EPI == EPI_ADD) load_residual_chunk(res_next, c0 + PCW, lane, out, row0 + q * 32, col0, c0 + PCW < 256 ? rows : 0, Cc, ldo);
+                drain_chunk<EPI, TO>(stage, taddr, c0, lane, out, row0 + q * 32, col0, rows, Cc, ldo, res);
+                if (EPI == EPI_ADD) {
+#pragma unroll
+                    for (int u = 0; u < RES_N; u++) res[u] = res_next[u];
+                }
             }
             tc_fence_before();
             __syncwarp();
