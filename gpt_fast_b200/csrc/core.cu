@@ -168,8 +168,8 @@ rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ pending,
 constexpr int NORM_VEC_MAX = 8;
 
 template <typename TW, typename TO>
-__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int D, float eps) {
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ pending, int S, size_t slice,
+                                   const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows, int D, float eps) {
     __shared__ float scratch[32];
     gfb_pdl_launch();
     const int r = blockIdx.x;
@@ -184,17 +184,36 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __rest
         for (int e = 0; e < 4; e++) wk[k][e] = i < nvec ? gfb_to_f32(w[4 * i + e]) : 0.f;
     }
     gfb_pdl_wait();
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+    const size_t row = (size_t)(rows ? rows[r] : r) * D;
+    float4* xr = reinterpret_cast<float4*>(x + row);
     float4 v[NORM_VEC_MAX];
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < NORM_VEC_MAX; k++) {
         int i = threadIdx.x + k * blockDim.x;
-        if (i < nvec) {
-            v[k] = xr[i];
-            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (pending != nullptr) {
+        // the row's pending partial sums, one after the other (ascending), each with all of a thread's loads in flight
+        for (int p = 0; p < S; p++) {
+            const float4* pr = reinterpret_cast<const float4*>(pending + (size_t)p * slice + row);
+            float4 a[NORM_VEC_MAX];
+#pragma unroll
+            for (int k = 0; k < NORM_VEC_MAX; k++) {
+                int i = threadIdx.x + k * blockDim.x;
+                a[k] = i < nvec ? pr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < NORM_VEC_MAX; k++) { v[k].x += a[k].x; v[k].y += a[k].y; v[k].z += a[k].z; v[k].w += a[k].w; }
+        }
+#pragma unroll
+        for (int k = 0; k < NORM_VEC_MAX; k++) {
+            int i = threadIdx.x + k * blockDim.x;
+            if (i < nvec) xr[i] = v[k];
         }
     }
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; k++) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
     ss = gfb_block_sum(ss, scratch);
     const float rstd = rsqrtf(ss / (float)D + eps);
 #pragma unroll
@@ -234,11 +253,11 @@ GFB_API int gfb_rmsnorm(float* x, const float* pending, int S, long slice, const
         return gfb_check(e, "gfb_rmsnorm (cluster)");
     }
     int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
-    if (pending == nullptr && D % 4 == 0 && D <= 4 * NORM_VEC_MAX * threads) {
+    if ((pending == nullptr || slice % 4 == 0) && D % 4 == 0 && D <= 4 * NORM_VEC_MAX * threads) {
         // few threads with many loads each: more rows are resident per SM and every thread has 8 loads in flight
         int vthreads = ((D / 4 + NORM_VEC_MAX - 1) / NORM_VEC_MAX + 31) / 32 * 32;
         if (vthreads < 64) vthreads = 64;
-#define VLAUNCH(TW, TO) e = gfb_launch(rmsnorm_vec_kernel<TW, TO>, dim3(R), dim3(vthreads), 0, stream, (const float*)x, (const TW*)w, (TO*)out, rows, D, eps)
+#define VLAUNCH(TW, TO) e = gfb_launch(rmsnorm_vec_kernel<TW, TO>, dim3(R), dim3(vthreads), 0, stream, x, pending, S, (size_t)slice, (const TW*)w, (TO*)out, rows, D, eps)
         if (w_dt == GFB_BF16 && out_dt == GFB_BF16) VLAUNCH(__nv_bfloat16, __nv_bfloat16);
         else if (w_dt == GFB_F32 && out_dt == GFB_BF16) VLAUNCH(float, __nv_bfloat16);
         else if (w_dt == GFB_BF16 && out_dt == GFB_F32) VLAUNCH(__nv_bfloat16, float);

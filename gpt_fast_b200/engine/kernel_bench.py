@@ -53,7 +53,7 @@ def bench_linear(a):
     gbs = N * K * 2 / us / 1e3
     tfs = 2.0 * M * N * K / us / 1e6
     print(f"linear M={M} N={N} K={K} mode={a.mode}: {us:.1f} us, weights at {gbs:.0f} GB/s, {tfs:.0f} TFLOP/s "
-          f"(plan swap,bn,splits,stages = {ops.kernels().tc_plan(M, N, K)})")
+          f"(plan swap,bn,splits,stages = {ops.kernels().tc_plan(M, N, K, a.mode)})")
 
 
 def paged_batch(batch, context, new, heads_kv, head_dim, device="cuda"):

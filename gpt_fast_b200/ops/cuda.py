@@ -203,11 +203,20 @@ class CudaKernels:
         """The tensor-core kernel takes rows of whole 16-byte units (TMA) and stores in 16-byte vectors."""
         return K % 8 == 0 and N % (16 if mode == "swiglu" else 8) == 0
 
-    def tc_plan(self, M, N, K):
+    def tc_plan(self, M, N, K, mode="store"):
         """(swap, bn, splits, stages) for the tensor-core product.  Few tokens: the weight rows fill the
         128 MMA rows and the tokens are its columns, split over K until about two blocks per SM stream
         weights; many tokens: 256 x 256 tiles on pairs of SMs (bn = 1024 names that kernel, 512 the
-        one-SM persistent kernel, 128/256 one tile per block)."""
+        one-SM persistent kernel, 128/256 one tile per block).  In between (129 to 512 tokens) a product
+        that may be split over K stays in the first form, with several column tiles of 128 tokens: one or two
+        row tiles of 256 x 256 leave most pairs of SMs idle unless the weight matrix is wide (measured at 256
+        tokens: q/k/v 26.8 -> 15.5 us, output projection 29.4 -> 12.8, down projection 78.1 -> 31.8; the
+        gate/up product with its SwiGLU cannot be split and is wide enough: 57 us on pairs, 78 us this way)."""
+        if 128 < M <= 512 and mode != "swiglu":
+            blocks = -(-N // 128) * -(-M // 128)
+            total_kb = -(-K // 64)
+            splits = max(1, min(total_kb // 8, (2 * self.sm_count) // blocks))
+            return 1, 128, splits, 3
         if M <= 128:
             bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
             blocks = -(-N // 128)
@@ -240,7 +249,7 @@ class CudaKernels:
     def _linear_tc(self, a, w, out, mode, plan=None, defer=False):
         M, K = a.shape
         N = w.shape[0]
-        swap, bn, splits, stages = plan or self.tc_plan(M, N, K)
+        swap, bn, splits, stages = plan or self.tc_plan(M, N, K, mode)
         ws = torch.empty(splits, M, N, dtype=torch.float32, device=a.device) if splits > 1 else None
         used = c_int(1)
         self._call("gemm_tc", "gfb_gemm_tc", _ptr(a), _ptr(w), _ptr(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),

@@ -12,7 +12,7 @@ from test_kernels_gpu import DEV, REF, make_batch, rnd
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("T,D,S", [(1, 64, 2), (8, 4096, 8), (5, 144, 3), (64, 1000, 4)])
+@pytest.mark.parametrize("T,D,S", [(1, 64, 2), (8, 4096, 8), (5, 144, 3), (64, 1000, 4), (300, 4096, 4), (200, 520, 3)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm_completes_a_pending_sum(T, D, S, out_dtype):
     x = rnd(T, D, scale=2.0)
@@ -37,7 +37,7 @@ def test_rmsnorm_completes_a_pending_sum(T, D, S, out_dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,q_lens,starts", [(4, 4, 16, [5, 11], [0, 3]), (6, 2, 24, [1, 1, 1], [0, 64, 130]),
-                                                 (32, 8, 128, [1] * 8, [128] * 8)])
+                                                 (32, 8, 128, [1] * 8, [128] * 8), (32, 8, 128, [200, 100], [0, 70])])
 def test_rope_append_from_partial_sums(dtype, H, G, d, q_lens, starts):
     batch, table, n_pages = make_batch(q_lens, starts, 9, 64, 8)
     T, W = batch.n_tokens, (H + 2 * G) * d
@@ -56,7 +56,8 @@ def test_rope_append_from_partial_sums(dtype, H, G, d, q_lens, starts):
     torch.testing.assert_close(pools[1].float(), pools[3].float(), **tol)
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (1, 6144, 4096), (64, 4096, 14336), (16, 512, 1024)])
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (1, 6144, 4096), (64, 4096, 14336), (16, 512, 1024),
+                                   (200, 4096, 4096), (384, 520, 1032), (512, 1000, 4096), (129, 264, 2048)])   # several column tiles of tokens
 def test_deferred_product_leaves_partial_sums(M, N, K):
     a = rnd(M, K, dtype=torch.bfloat16)
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.02, seed=1)
