@@ -211,8 +211,9 @@ class CudaKernels:
         that may be split over K stays in the first form, with several column tiles of 128 tokens: one or two
         row tiles of 256 x 256 leave most pairs of SMs idle unless the weight matrix is wide (measured at 256
         tokens: q/k/v 26.8 -> 15.5 us, output projection 29.4 -> 12.8, down projection 78.1 -> 31.8; the
-        gate/up product with its SwiGLU cannot be split and is wide enough: 57 us on pairs, 78 us this way)."""
-        if 128 < M <= 512 and mode != "swiglu":
+        gate/up product with its SwiGLU cannot be split and is wide enough: 57 us on pairs, 78 us this way; so is
+        the output product: 224 us on pairs, 383 us this way, hence the count of 256 x 256 tiles in the rule)."""
+        if 128 < M <= 512 and mode != "swiglu" and -(-M // 256) * -(-N // 256) < self.sm_count // 2:
             blocks = -(-N // 128) * -(-M // 128)
             total_kb = -(-K // 64)
             splits = max(1, min(total_kb // 8, (2 * self.sm_count) // blocks))
