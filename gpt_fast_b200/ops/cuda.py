@@ -40,7 +40,14 @@ def _need(t: torch.Tensor, dtype=None, shape=None, name="tensor"):
         _fail(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream of the current device as a handle for the kernels.  Asked for at every launch (a capture
+    runs on a stream of its own); the short way through torch's C module costs a tenth of `current_stream()`."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
