@@ -784,7 +784,8 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
     // Tile pairs per block: five where the grid covers at most a quarter of the SMs (a short context is then requested
     // all at once; with more blocks than that, one block of five pairs per SM leaves no room for the blocks of the
     // product behind it, which want to fetch their weights meanwhile: 8 sequences x 8 heads, 2.99 -> 2.92 ms per step);
-    // two where more than three blocks per SM wait with a few pages each (three blocks then fit an SM and their
+    // two where more than two blocks per SM wait with a few pages each (three blocks then fit an SM, which saves a
+    // round of blocks between two and three per SM: 48 sequences x 8 heads of 200 tokens, 12.0 -> 8.1 us; and their
     // set-ups and merges overlap: 40 heads of their own keys at batch 32, 42 -> 38 us; 8 groups at batch 64 and 150
     // tokens, 14.5 -> 12.6 us); three otherwise (long slices want two pages in flight behind the one being worked on).
     static const Kern kerns[3][2][3] = {
@@ -808,7 +809,7 @@ cudaError_t launch_decode_mma(int d, int src, dim3 grid, cudaStream_t stream, co
     }
     const int di = d == 128 ? 1 : 0;
     const long blocks = (long)grid.x * grid.y * grid.z;
-    const int few = blocks <= sms / 4 ? 1 : (blocks > 3L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
+    const int few = blocks <= sms / 4 ? 1 : (blocks > 2L * sms && pages_per_slice > 0 && pages_per_slice <= 6) ? 2 : 0;
     const int nbuf = few == 1 ? DECODE_NBUF_FEW : few == 2 ? DECODE_NBUF_SHORT : DECODE_NBUF_MANY;
     // alignment slack, tiles, q rows, barriers and a flag
     const size_t msmem = 1024 + (size_t)2 * nbuf * PAGE * d * 2 + (size_t)8 * (d + 8) * 2 + 8 * nbuf + 16;
